@@ -1,0 +1,61 @@
+"""Build the native extension in-tree: ``python -m elf_b200.csrc.build``.
+
+nvcc cross-compiles for sm_100a without a GPU; the resulting shared object stays next to
+the sources (``elf_b200/csrc/_build``) so it ships with the tree to GPU machines.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+BUILD_DIR = HERE / "_build"
+NAME = "elf_b200_C"
+SOURCES = ["bindings.cpp", "fused_bindings.cpp", "host_runtime.cpp", "gemm_sm100.cu", "fused_ops.cu"]
+OPTIONAL_SOURCES = ["attention_sm100.cu", "attention_bindings.cpp", "dp_reduce.cu", "dp_reduce_bindings.cpp"]
+NVCC_FLAGS = [
+    "-gencode",
+    "arch=compute_100a,code=sm_100a",
+    "-lineinfo",
+    "-O3",
+    "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "--use_fast_math",
+]
+
+
+def sources():
+    out = [str(HERE / s) for s in SOURCES]
+    out += [str(HERE / s) for s in OPTIONAL_SOURCES if (HERE / s).exists()]
+    return out
+
+
+def build(verbose: bool = False):
+    """Compile (incrementally, through ninja) and import the extension module."""
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 1)))
+    from torch.utils import cpp_extension
+
+    BUILD_DIR.mkdir(exist_ok=True)
+    defines = []
+    if (HERE / "attention_sm100.cu").exists():
+        defines.append("-DELFB_WITH_ATTENTION")
+    if (HERE / "dp_reduce.cu").exists():
+        defines.append("-DELFB_WITH_DP_REDUCE")
+    return cpp_extension.load(
+        name=NAME,
+        sources=sources(),
+        extra_cflags=["-O3", "-std=c++17"] + defines,
+        extra_cuda_cflags=NVCC_FLAGS + defines,
+        extra_ldflags=["-lcudart"],
+        build_directory=str(BUILD_DIR),
+        with_cuda=True,
+        verbose=verbose,
+    )
+
+
+if __name__ == "__main__":
+    mod = build(verbose="-v" in sys.argv)
+    print("built", mod.__file__)

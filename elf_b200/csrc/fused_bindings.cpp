@@ -1,0 +1,190 @@
+// torch glue for fused_ops.cu: shape checks, output allocation, stream selection.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "fused_ops.h"
+
+namespace {
+
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream(); }
+
+void check(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, "elf_b200 ", what, ": ", cudaGetErrorString(e)); }
+
+void need_bf16(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), name, " must be a contiguous CUDA bf16 tensor");
+}
+
+// returns (y, rstd, h) where h = x + residual (or x itself when residual is None)
+std::tuple<at::Tensor, at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps,
+                                                            const c10::optional<at::Tensor>& residual) {
+  need_bf16(x, "x");
+  need_bf16(w, "weight");
+  c10::cuda::CUDAGuard g(x.device());
+  const int dim = (int)x.size(-1);
+  const int rows = (int)(x.numel() / dim);
+  TORCH_CHECK(w.numel() == dim, "weight must have ", dim, " elements");
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  at::Tensor h = x;
+  const void* res = nullptr;
+  if (residual.has_value() && residual->defined()) {
+    need_bf16(*residual, "residual");
+    TORCH_CHECK(residual->sizes() == x.sizes(), "residual must match x");
+    h = at::empty_like(x);
+    res = residual->data_ptr();
+  }
+  check(elfb::rmsnorm_forward(x.data_ptr(), res, w.data_ptr(), y.data_ptr(), res ? h.data_ptr() : nullptr,
+                              rstd.data_ptr<float>(), rows, dim, (float)eps, cur()),
+        "rmsnorm_forward");
+  return {y, rstd, h};
+}
+
+// returns dx; dw (fp32 [dim]) is written or accumulated in place.  `scratch` may be passed to avoid an allocation.
+at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd, at::Tensor& dw,
+                       bool accumulate_dw, const c10::optional<at::Tensor>& dres, const c10::optional<at::Tensor>& scratch) {
+  need_bf16(dy, "dy");
+  need_bf16(x, "x");
+  need_bf16(w, "weight");
+  c10::cuda::CUDAGuard g(x.device());
+  const int dim = (int)x.size(-1);
+  const int rows = (int)(x.numel() / dim);
+  TORCH_CHECK(dw.scalar_type() == at::kFloat && dw.numel() == dim && dw.is_contiguous(), "dw must be fp32 [dim]");
+  const int nb = elfb::rmsnorm_backward_blocks(rows);
+  at::Tensor part = (scratch.has_value() && scratch->defined()) ? *scratch : at::empty({(int64_t)nb * dim}, x.options().dtype(at::kFloat));
+  TORCH_CHECK(part.numel() >= (int64_t)nb * dim && part.scalar_type() == at::kFloat, "scratch too small");
+  auto dx = at::empty_like(x);
+  const void* dr = nullptr;
+  if (dres.has_value() && dres->defined()) {
+    need_bf16(*dres, "dres");
+    dr = dres->data_ptr();
+  }
+  check(elfb::rmsnorm_backward(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
+                               part.data_ptr<float>(), dw.data_ptr<float>(), accumulate_dw, rows, dim, cur()),
+        "rmsnorm_backward");
+  return dx;
+}
+
+void rope_(at::Tensor& x, const at::Tensor& cos_t, const at::Tensor& sin_t, int64_t n_rot_heads, int64_t head_dim,
+           int64_t seq_len, bool backward) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "x must be a 2-D bf16 CUDA matrix");
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat && cos_t.is_contiguous() && sin_t.is_contiguous(),
+              "cos/sin tables must be contiguous fp32");
+  TORCH_CHECK(cos_t.size(0) >= seq_len && cos_t.size(1) == head_dim / 2, "cos/sin tables must be [>=seq_len, head_dim/2]");
+  TORCH_CHECK(n_rot_heads * head_dim <= x.size(1), "more rotary heads than columns");
+  c10::cuda::CUDAGuard g(x.device());
+  check(elfb::rope_inplace(x.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), (int)x.size(0), (int)x.stride(0),
+                           (int)n_rot_heads, (int)head_dim, (int)seq_len, backward ? -1.f : 1.f, cur()),
+        "rope");
+}
+
+at::Tensor swiglu_fwd(const at::Tensor& gu) {
+  need_bf16(gu, "gate_up");
+  c10::cuda::CUDAGuard g(gu.device());
+  const int f = (int)gu.size(-1) / 2;
+  const int rows = (int)(gu.numel() / (2 * f));
+  auto sizes = gu.sizes().vec();
+  sizes.back() = f;
+  auto out = at::empty(sizes, gu.options());
+  check(elfb::swiglu_forward(gu.data_ptr(), out.data_ptr(), rows, f, cur()), "swiglu_forward");
+  return out;
+}
+at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& gu) {
+  need_bf16(dout, "dout");
+  need_bf16(gu, "gate_up");
+  c10::cuda::CUDAGuard g(gu.device());
+  const int f = (int)gu.size(-1) / 2;
+  const int rows = (int)(gu.numel() / (2 * f));
+  auto dgu = at::empty_like(gu);
+  check(elfb::swiglu_backward(dout.data_ptr(), gu.data_ptr(), dgu.data_ptr(), rows, f, cur()), "swiglu_backward");
+  return dgu;
+}
+
+// returns (loss per row fp32, lse per row fp32)
+std::tuple<at::Tensor, at::Tensor> ce_fwd(const at::Tensor& logits, const at::Tensor& targets, int64_t ignore_index) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be a 2-D bf16 CUDA matrix");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0), "targets must be int64 [rows]");
+  c10::cuda::CUDAGuard g(logits.device());
+  auto loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  auto lse = at::empty_like(loss);
+  check(elfb::cross_entropy_forward(logits.data_ptr(), targets.data_ptr<int64_t>(), loss.data_ptr<float>(), lse.data_ptr<float>(),
+                                    (int)logits.size(0), (int)logits.size(1), logits.stride(0), ignore_index, cur()),
+        "cross_entropy_forward");
+  return {loss, lse};
+}
+// writes dlogits over `out` (pass logits itself for the in-place form)
+void ce_bwd(const at::Tensor& logits, at::Tensor& out, const at::Tensor& targets, const at::Tensor& lse,
+            const c10::optional<at::Tensor>& gscale, double scale, int64_t ignore_index) {
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.sizes() == logits.sizes() && out.stride(0) == logits.stride(0), "out must match logits");
+  c10::cuda::CUDAGuard g(logits.device());
+  const float* gs = nullptr;
+  if (gscale.has_value() && gscale->defined()) {
+    TORCH_CHECK(gscale->scalar_type() == at::kFloat && gscale->numel() == 1, "gscale must be one fp32 value");
+    gs = gscale->data_ptr<float>();
+  }
+  check(elfb::cross_entropy_backward(logits.data_ptr(), out.data_ptr(), targets.data_ptr<int64_t>(), lse.data_ptr<float>(), gs,
+                                     (float)scale, (int)logits.size(0), (int)logits.size(1), logits.stride(0), ignore_index, cur()),
+        "cross_entropy_backward");
+}
+
+at::Tensor embedding_fwd(const at::Tensor& table, const at::Tensor& ids) {
+  need_bf16(table, "table");
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.is_cuda(), "ids must be contiguous int64 CUDA");
+  c10::cuda::CUDAGuard g(table.device());
+  auto sizes = ids.sizes().vec();
+  sizes.push_back(table.size(1));
+  auto out = at::empty(sizes, table.options());
+  check(elfb::embedding_forward(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), (int)ids.numel(), (int)table.size(1), cur()),
+        "embedding_forward");
+  return out;
+}
+void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dtable) {
+  need_bf16(dout, "dout");
+  TORCH_CHECK(dtable.is_contiguous() && (dtable.scalar_type() == at::kFloat || dtable.scalar_type() == at::kBFloat16), "dtable must be fp32 or bf16");
+  c10::cuda::CUDAGuard g(dout.device());
+  check(elfb::embedding_backward(dout.data_ptr(), ids.data_ptr<int64_t>(), dtable.data_ptr(), dtable.scalar_type() == at::kFloat,
+                                 (int)ids.numel(), (int)dtable.size(1), cur()),
+        "embedding_backward");
+}
+
+void adamw(at::Tensor& p, const at::Tensor& grad, at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double b1, double b2,
+           double eps, double wd, int64_t step, double grad_scale) {
+  need_bf16(p, "param");
+  TORCH_CHECK(grad.is_contiguous() && grad.numel() == p.numel(), "grad must be contiguous and match param");
+  TORCH_CHECK(grad.scalar_type() == at::kFloat || grad.scalar_type() == at::kBFloat16, "grad must be fp32 or bf16");
+  for (const at::Tensor* t : {&master, &m, &v})
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == p.numel(), "optimizer state must be contiguous fp32");
+  c10::cuda::CUDAGuard g(p.device());
+  const double bc1 = 1.0 - std::pow(b1, (double)step), bc2 = 1.0 - std::pow(b2, (double)step);
+  check(elfb::adamw_step(p.data_ptr(), grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr<float>(),
+                         v.data_ptr<float>(), p.numel(), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1, (float)bc2,
+                         (float)grad_scale, cur()),
+        "adamw_step");
+}
+
+void scale_(at::Tensor& x, double a) {
+  need_bf16(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  check(elfb::scale_bf16(x.data_ptr(), x.numel(), (float)a, cur()), "scale");
+}
+
+}  // namespace
+
+void register_fused_ops(pybind11::module_& m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("weight"), py::arg("eps"), py::arg("residual") = c10::nullopt);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("weight"), py::arg("rstd"), py::arg("dw"),
+        py::arg("accumulate_dw") = false, py::arg("dres") = c10::nullopt, py::arg("scratch") = c10::nullopt);
+  m.def("rmsnorm_bwd_blocks", &elfb::rmsnorm_backward_blocks);
+  m.def("rope_", &rope_, py::arg("x"), py::arg("cos"), py::arg("sin"), py::arg("n_rot_heads"), py::arg("head_dim"),
+        py::arg("seq_len"), py::arg("backward") = false);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_fwd", &ce_fwd, py::arg("logits"), py::arg("targets"), py::arg("ignore_index") = -100);
+  m.def("ce_bwd", &ce_bwd, py::arg("logits"), py::arg("out"), py::arg("targets"), py::arg("lse"), py::arg("gscale") = c10::nullopt,
+        py::arg("scale") = 1.0, py::arg("ignore_index") = -100);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("adamw", &adamw, py::arg("param"), py::arg("grad"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("lr"),
+        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0);
+  m.def("scale_", &scale_);
+}

@@ -1,0 +1,556 @@
+// Bandwidth-bound kernels for sm_100a: RMSNorm, RoPE, SwiGLU, cross-entropy, embedding,
+// AdamW.  All move 16 bytes per thread per access and keep fp32 math in registers; the
+// roofline for each is HBM traffic only.
+#include "fused_ops.h"
+
+#include <cuda_bf16.h>
+
+namespace elfb {
+
+namespace {
+
+struct alignas(16) Bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const Bf16x8& p, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ Bf16x8 pack8(const float (&f)[8]) {
+  Bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; every thread gets the result.  `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nwarps ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nwarps ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// ------------------------------------------------------------------------------ RMSNorm
+constexpr int RMS_THREADS = 256;
+constexpr int RMS_MAX_VEC = 4;  // rows up to 256*4*8 = 8192 elements stay in registers
+
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_fwd_kernel(const Bf16x8* __restrict__ x, const Bf16x8* __restrict__ res,
+                                                                  const Bf16x8* __restrict__ w, Bf16x8* __restrict__ y,
+                                                                  Bf16x8* __restrict__ h, float* __restrict__ rstd, int dim8,
+                                                                  float inv_dim, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const Bf16x8* xr = x + row * dim8;
+  float vals[RMS_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < RMS_MAX_VEC; ++it) {
+    const int i = threadIdx.x + it * RMS_THREADS;
+    if (i < dim8) {
+      unpack8(xr[i], vals[it]);
+      if (RESIDUAL) {
+        float r[8];
+        unpack8(res[row * dim8 + i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[it][j] += r[j];
+        const Bf16x8 hv = pack8(vals[it]);
+        h[row * dim8 + i] = hv;
+        unpack8(hv, vals[it]);  // normalise exactly what later passes will read back
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[it][j] * vals[it][j];
+    }
+  }
+  for (int i = threadIdx.x + RMS_MAX_VEC * RMS_THREADS; i < dim8; i += RMS_THREADS) {  // very wide rows
+    float t[8];
+    unpack8(xr[i], t);
+    if (RESIDUAL) {
+      float r[8];
+      unpack8(res[row * dim8 + i], r);
+      for (int j = 0; j < 8; ++j) t[j] += r[j];
+      const Bf16x8 hv = pack8(t);
+      h[row * dim8 + i] = hv;
+      unpack8(hv, t);
+    }
+    for (int j = 0; j < 8; ++j) ss += t[j] * t[j];
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss * inv_dim + eps);
+  if (threadIdx.x == 0) rstd[row] = rs;
+#pragma unroll
+  for (int it = 0; it < RMS_MAX_VEC; ++it) {
+    const int i = threadIdx.x + it * RMS_THREADS;
+    if (i < dim8) {
+      float wv[8], o[8];
+      unpack8(w[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[it][j] * rs * wv[j];
+      y[row * dim8 + i] = pack8(o);
+    }
+  }
+  for (int i = threadIdx.x + RMS_MAX_VEC * RMS_THREADS; i < dim8; i += RMS_THREADS) {
+    float t[8], wv[8], o[8];
+    unpack8(RESIDUAL ? h[row * dim8 + i] : xr[i], t);
+    unpack8(w[i], wv);
+    for (int j = 0; j < 8; ++j) o[j] = t[j] * rs * wv[j];
+    y[row * dim8 + i] = pack8(o);
+  }
+}
+
+// Each block walks rows block, block+grid, ... ; per row: dx; per column: partial dw in registers.
+constexpr int RMS_BWD_BLOCKS = 296;  // 2 per SM
+
+template <bool DRES>
+__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
+                                                                  const Bf16x8* __restrict__ w, const float* __restrict__ rstd,
+                                                                  const Bf16x8* __restrict__ dres, Bf16x8* __restrict__ dx,
+                                                                  float* __restrict__ dw_partial, int rows, int dim8,
+                                                                  float inv_dim) {
+  __shared__ float red[32];
+  float wv[RMS_MAX_VEC][8], dwacc[RMS_MAX_VEC][8];
+#pragma unroll
+  for (int it = 0; it < RMS_MAX_VEC; ++it) {
+    const int i = threadIdx.x + it * RMS_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[it][j] = 0.f;
+    if (i < dim8) unpack8(w[i], wv[it]);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rs = rstd[row];
+    float xv[RMS_MAX_VEC][8], gv[RMS_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int it = 0; it < RMS_MAX_VEC; ++it) {
+      const int i = threadIdx.x + it * RMS_THREADS;
+      if (i < dim8) {
+        unpack8(x[row * dim8 + i], xv[it]);
+        unpack8(dy[row * dim8 + i], gv[it]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[it][j] += gv[it][j] * xv[it][j] * rs;
+          gv[it][j] *= wv[it][j];
+          dot += gv[it][j] * xv[it][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red);
+    const float c = dot * inv_dim * rs * rs * rs;
+#pragma unroll
+    for (int it = 0; it < RMS_MAX_VEC; ++it) {
+      const int i = threadIdx.x + it * RMS_THREADS;
+      if (i < dim8) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gv[it][j] * rs - xv[it][j] * c;
+        if (DRES) {
+          float r[8];
+          unpack8(dres[row * dim8 + i], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        dx[row * dim8 + i] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < RMS_MAX_VEC; ++it) {
+    const int i = threadIdx.x + it * RMS_THREADS;
+    if (i < dim8) {
+      float* dst = dw_partial + (long long)blockIdx.x * dim8 * 8 + (long long)i * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[it][0], dwacc[it][1], dwacc[it][2], dwacc[it][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[it][4], dwacc[it][5], dwacc[it][6], dwacc[it][7]);
+    }
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int dim, bool accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * dim + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ------------------------------------------------------------------------------ RoPE
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            long long total, int row_stride, int n_rot_heads, int half, int seq_len, float sign) {
+  // one thread rotates 8 consecutive pairs (i, i + half) of one head
+  const int vec_per_head = half / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int v = idx % vec_per_head;
+  const int head = (idx / vec_per_head) % n_rot_heads;
+  const long long row = idx / ((long long)vec_per_head * n_rot_heads);
+  const int pos = row % seq_len;
+  __nv_bfloat16* base = x + row * row_stride + head * (2 * half) + v * 8;
+  Bf16x8 lo = *reinterpret_cast<Bf16x8*>(base), hi = *reinterpret_cast<Bf16x8*>(base + half);
+  float a[8], b[8], oa[8], ob[8];
+  unpack8(lo, a);
+  unpack8(hi, b);
+  const float4* c4 = reinterpret_cast<const float4*>(cos_t + (long long)pos * half + v * 8);
+  const float4* s4 = reinterpret_cast<const float4*>(sin_t + (long long)pos * half + v * 8);
+  const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+  const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float s = sn[j] * sign;
+    oa[j] = a[j] * cs[j] - b[j] * s;
+    ob[j] = b[j] * cs[j] + a[j] * s;
+  }
+  *reinterpret_cast<Bf16x8*>(base) = pack8(oa);
+  *reinterpret_cast<Bf16x8*>(base + half) = pack8(ob);
+}
+
+// ------------------------------------------------------------------------------ SwiGLU
+__global__ void swiglu_fwd_kernel(const Bf16x8* __restrict__ gu, Bf16x8* __restrict__ out, long long total, int f8) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long row = idx / f8;
+  const int c = idx % f8;
+  float g[8], u[8], o[8];
+  unpack8(gu[row * 2 * f8 + c], g);
+  unpack8(gu[row * 2 * f8 + f8 + c], u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  out[idx] = pack8(o);
+}
+__global__ void swiglu_bwd_kernel(const Bf16x8* __restrict__ dout, const Bf16x8* __restrict__ gu, Bf16x8* __restrict__ dgu,
+                                  long long total, int f8) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long row = idx / f8;
+  const int c = idx % f8;
+  float g[8], u[8], d[8], dg[8], du[8];
+  unpack8(gu[row * 2 * f8 + c], g);
+  unpack8(gu[row * 2 * f8 + f8 + c], u);
+  unpack8(dout[idx], d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sg = 1.f / (1.f + __expf(-g[j]));
+    const float silu = g[j] * sg;
+    dg[j] = d[j] * u[j] * (sg + silu * (1.f - sg));
+    du[j] = d[j] * silu;
+  }
+  dgu[row * 2 * f8 + c] = pack8(dg);
+  dgu[row * 2 * f8 + f8 + c] = pack8(du);
+}
+
+// ------------------------------------------------------------------------------ cross entropy
+constexpr int CE_THREADS = 1024;
+
+__global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                            const int64_t* __restrict__ targets, float* __restrict__ loss,
+                                                            float* __restrict__ lse_out, int vocab, long long ld,
+                                                            int64_t ignore_index) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  const int v8 = vocab / 8;
+  // online softmax: running max m and sum s of exp(x - m)
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < v8; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(lr)[i], f);
+    float cm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) cm = fmaxf(cm, f[j]);
+    const float nm = fmaxf(m, cm);
+    float add = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + add;
+    m = nm;
+  }
+  for (int i = v8 * 8 + threadIdx.x; i < vocab; i += CE_THREADS) {
+    const float f = __bfloat162float(lr[i]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  const float gm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float lse = gm + logf(gs);
+    lse_out[row] = lse;
+    const int64_t t = targets[row];
+    loss[row] = (t == ignore_index || t < 0 || t >= vocab) ? 0.f : lse - __bfloat162float(lr[t]);
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(const __nv_bfloat16* __restrict__ logits,
+                                                            __nv_bfloat16* __restrict__ dlogits,
+                                                            const int64_t* __restrict__ targets, const float* __restrict__ lse,
+                                                            const float* __restrict__ gscale, float scale, int vocab,
+                                                            long long ld, int64_t ignore_index) {
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  __nv_bfloat16* dr = dlogits + row * ld;
+  const int64_t t = targets[row];
+  const bool ignored = (t == ignore_index || t < 0 || t >= vocab);
+  const float g = ignored ? 0.f : (gscale ? gscale[0] : 1.f) * scale;
+  const float l = lse[row];
+  const int v8 = vocab / 8;
+  for (int i = threadIdx.x; i < v8; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(lr)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = __expf(f[j] - l);
+      f[j] = (p - ((long long)i * 8 + j == t ? 1.f : 0.f)) * g;
+    }
+    reinterpret_cast<Bf16x8*>(dr)[i] = pack8(f);
+  }
+  for (int i = v8 * 8 + threadIdx.x; i < vocab; i += CE_THREADS) {
+    const float p = __expf(__bfloat162float(lr[i]) - l);
+    dr[i] = __float2bfloat16((p - (i == t ? 1.f : 0.f)) * g);
+  }
+}
+
+// ------------------------------------------------------------------------------ embedding
+__global__ void embedding_fwd_kernel(const Bf16x8* __restrict__ table, const int64_t* __restrict__ ids, Bf16x8* __restrict__ out,
+                                     long long total, int dim8) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long row = idx / dim8;
+  const int c = idx % dim8;
+  out[idx] = table[ids[row] * dim8 + c];
+}
+template <bool F32>
+__global__ void embedding_bwd_kernel(const __nv_bfloat162* __restrict__ dout, const int64_t* __restrict__ ids, void* __restrict__ dtable,
+                                     long long total, int dim2) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long row = idx / dim2;
+  const int c = idx % dim2;
+  const __nv_bfloat162 g = dout[idx];
+  if (F32) {
+    float* d = reinterpret_cast<float*>(dtable) + (ids[row] * dim2 + c) * 2;
+    const float2 f = __bfloat1622float2(g);
+    atomicAdd(d, f.x);
+    atomicAdd(d + 1, f.y);
+  } else {
+    atomicAdd(reinterpret_cast<__nv_bfloat162*>(dtable) + ids[row] * dim2 + c, g);
+  }
+}
+
+// ------------------------------------------------------------------------------ AdamW
+template <bool GRAD_F32>
+__global__ void adamw_kernel(Bf16x8* __restrict__ p, const void* __restrict__ grad, float* __restrict__ master,
+                             float* __restrict__ m, float* __restrict__ v, long long n8, long long n, float lr, float b1,
+                             float b2, float eps, float decay, float inv_bc1, float inv_bc2, float gscale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const long long base = i * 8;
+  float g[8];
+  if (base + 8 <= n) {
+    if (GRAD_F32) {
+      const float4 a = reinterpret_cast<const float4*>(grad)[2 * i], b = reinterpret_cast<const float4*>(grad)[2 * i + 1];
+      g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+    } else {
+      unpack8(reinterpret_cast<const Bf16x8*>(grad)[i], g);
+    }
+    float4 w0 = reinterpret_cast<float4*>(master)[2 * i], w1 = reinterpret_cast<float4*>(master)[2 * i + 1];
+    float4 m0 = reinterpret_cast<float4*>(m)[2 * i], m1 = reinterpret_cast<float4*>(m)[2 * i + 1];
+    float4 v0 = reinterpret_cast<float4*>(v)[2 * i], v1 = reinterpret_cast<float4*>(v)[2 * i + 1];
+    float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * gscale;
+      mm[j] = b1 * mm[j] + (1.f - b1) * gj;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+      const float upd = (mm[j] * inv_bc1) / (sqrtf(vv[j] * inv_bc2) + eps);
+      w[j] = w[j] * decay - lr * upd;
+    }
+    reinterpret_cast<float4*>(master)[2 * i] = make_float4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<float4*>(master)[2 * i + 1] = make_float4(w[4], w[5], w[6], w[7]);
+    reinterpret_cast<float4*>(m)[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    reinterpret_cast<float4*>(v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    p[i] = pack8(w);
+  } else {
+    for (long long k = base; k < n; ++k) {  // ragged tail
+      const float gj = (GRAD_F32 ? reinterpret_cast<const float*>(grad)[k]
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grad)[k])) * gscale;
+      const float mk = b1 * m[k] + (1.f - b1) * gj;
+      const float vk = b2 * v[k] + (1.f - b2) * gj * gj;
+      const float wk = master[k] * decay - lr * (mk * inv_bc1) / (sqrtf(vk * inv_bc2) + eps);
+      m[k] = mk; v[k] = vk; master[k] = wk;
+      reinterpret_cast<__nv_bfloat16*>(p)[k] = __float2bfloat16(wk);
+    }
+  }
+}
+
+__global__ void scale_bf16_kernel(Bf16x8* __restrict__ x, long long n8, long long n, float a) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  if (i * 8 + 8 <= n) {
+    float f[8];
+    unpack8(x[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] *= a;
+    x[i] = pack8(f);
+  } else {
+    __nv_bfloat16* t = reinterpret_cast<__nv_bfloat16*>(x);
+    for (long long k = i * 8; k < n; ++k) t[k] = __float2bfloat16(__bfloat162float(t[k]) * a);
+  }
+}
+
+inline int blocks_for(long long n, int threads) { return (int)((n + threads - 1) / threads); }
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ launchers
+
+cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, void* y, void* h, float* rstd, int rows,
+                            int dim, float eps, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (dim % 8) return cudaErrorInvalidValue;
+  const int dim8 = dim / 8;
+  if (residual)
+    rmsnorm_fwd_kernel<true><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)x, (const Bf16x8*)residual, (const Bf16x8*)w,
+                                                          (Bf16x8*)y, (Bf16x8*)h, rstd, dim8, 1.f / dim, eps);
+  else
+    rmsnorm_fwd_kernel<false><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)x, nullptr, (const Bf16x8*)w, (Bf16x8*)y, nullptr,
+                                                           rstd, dim8, 1.f / dim, eps);
+  return cudaGetLastError();
+}
+
+int rmsnorm_backward_blocks(int rows) { return rows < RMS_BWD_BLOCKS ? (rows > 0 ? rows : 1) : RMS_BWD_BLOCKS; }
+
+cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
+                             float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (dim % 8 || dim > RMS_THREADS * RMS_MAX_VEC * 8) return cudaErrorInvalidValue;
+  const int dim8 = dim / 8, nb = rmsnorm_backward_blocks(rows);
+  if (dres_in)
+    rmsnorm_bwd_kernel<true><<<nb, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd,
+                                                        (const Bf16x8*)dres_in, (Bf16x8*)dx, dw_partial, rows, dim8, 1.f / dim);
+  else
+    rmsnorm_bwd_kernel<false><<<nb, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr,
+                                                         (Bf16x8*)dx, dw_partial, rows, dim8, 1.f / dim);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, dw, nb, dim, accumulate_dw);
+  return cudaGetLastError();
+}
+
+cudaError_t rope_inplace(void* x, const float* cos_t, const float* sin_t, int rows, int row_stride, int n_rot_heads,
+                         int head_dim, int seq_len, float sign, cudaStream_t s) {
+  const int half = head_dim / 2;
+  if (half % 8 || row_stride % 8) return cudaErrorInvalidValue;
+  const long long total = (long long)rows * n_rot_heads * (half / 8);
+  if (total == 0) return cudaSuccess;
+  rope_kernel<<<blocks_for(total, 256), 256, 0, s>>>((__nv_bfloat16*)x, cos_t, sin_t, total, row_stride, n_rot_heads, half,
+                                                     seq_len, sign);
+  return cudaGetLastError();
+}
+
+cudaError_t swiglu_forward(const void* gu, void* out, int rows, int f, cudaStream_t s) {
+  if (f % 8) return cudaErrorInvalidValue;
+  const long long total = (long long)rows * (f / 8);
+  if (total == 0) return cudaSuccess;
+  swiglu_fwd_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)gu, (Bf16x8*)out, total, f / 8);
+  return cudaGetLastError();
+}
+cudaError_t swiglu_backward(const void* dout, const void* gu, void* dgu, int rows, int f, cudaStream_t s) {
+  if (f % 8) return cudaErrorInvalidValue;
+  const long long total = (long long)rows * (f / 8);
+  if (total == 0) return cudaSuccess;
+  swiglu_bwd_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)dout, (const Bf16x8*)gu, (Bf16x8*)dgu, total, f / 8);
+  return cudaGetLastError();
+}
+
+cudaError_t cross_entropy_forward(const void* logits, const int64_t* targets, float* loss, float* lse, int rows, int vocab,
+                                  long long ld, int64_t ignore_index, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (ld % 8) return cudaErrorInvalidValue;
+  ce_fwd_kernel<<<rows, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, targets, loss, lse, vocab, ld, ignore_index);
+  return cudaGetLastError();
+}
+cudaError_t cross_entropy_backward(const void* logits, void* dlogits, const int64_t* targets, const float* lse,
+                                   const float* gscale, float scale, int rows, int vocab, long long ld, int64_t ignore_index,
+                                   cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (ld % 8) return cudaErrorInvalidValue;
+  ce_bwd_kernel<<<rows, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, (__nv_bfloat16*)dlogits, targets, lse, gscale, scale,
+                                            vocab, ld, ignore_index);
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s) {
+  if (dim % 8) return cudaErrorInvalidValue;
+  const long long total = (long long)rows * (dim / 8);
+  if (total == 0) return cudaSuccess;
+  embedding_fwd_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)table, ids, (Bf16x8*)out, total, dim / 8);
+  return cudaGetLastError();
+}
+cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim,
+                               cudaStream_t s) {
+  if (dim % 2) return cudaErrorInvalidValue;
+  const long long total = (long long)rows * (dim / 2);
+  if (total == 0) return cudaSuccess;
+  if (dtable_f32)
+    embedding_bwd_kernel<true><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
+  else
+    embedding_bwd_kernel<false><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
+  return cudaGetLastError();
+}
+
+cudaError_t adamw_step(void* p_bf16, const void* grad, bool grad_f32, float* master, float* m, float* v, long long n,
+                       float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                       float grad_scale, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const long long n8 = (n + 7) / 8;
+  const float decay = 1.f - lr * weight_decay;
+  if (grad_f32)
+    adamw_kernel<true><<<blocks_for(n8, 256), 256, 0, s>>>((Bf16x8*)p_bf16, grad, master, m, v, n8, n, lr, beta1, beta2, eps,
+                                                           decay, 1.f / bc1, 1.f / bc2, grad_scale);
+  else
+    adamw_kernel<false><<<blocks_for(n8, 256), 256, 0, s>>>((Bf16x8*)p_bf16, grad, master, m, v, n8, n, lr, beta1, beta2, eps,
+                                                            decay, 1.f / bc1, 1.f / bc2, grad_scale);
+  return cudaGetLastError();
+}
+
+cudaError_t scale_bf16(void* x, long long n, float a, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const long long n8 = (n + 7) / 8;
+  scale_bf16_kernel<<<blocks_for(n8, 256), 256, 0, s>>>((Bf16x8*)x, n8, n, a);
+  return cudaGetLastError();
+}
+
+}  // namespace elfb

@@ -1,0 +1,53 @@
+// Launchers of the bandwidth-bound sm_100a kernels (fused_ops.cu).  All pointers are device
+// pointers; 16-bit activations are bf16 unless `fp16` is set; every launcher returns the
+// CUDA error of its launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace elfb {
+
+// y = (x [+ residual]) * rsqrt(mean(.^2) + eps) * w ; optionally writes h = x + residual.
+cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, void* y, void* h, float* rstd, int rows,
+                            int dim, float eps, cudaStream_t s);
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) [+ dres_in]; dw_partial[block][dim] = sum over the block's rows of dy*x*rstd.
+// `dw_partial` is scratch of rmsnorm_backward_blocks(rows) * dim floats; `dw` (fp32 [dim]) receives (+=) the column sums.
+int rmsnorm_backward_blocks(int rows);
+cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
+                             float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s);
+
+// In-place rotary embedding on the first `n_rot_heads` heads of a [rows][n_heads*head_dim] bf16 matrix;
+// position = row % seq_len; cos/sin tables are fp32 [seq_len][head_dim/2]; sign = +1 forward, -1 backward.
+cudaError_t rope_inplace(void* x, const float* cos_t, const float* sin_t, int rows, int row_stride, int n_rot_heads,
+                         int head_dim, int seq_len, float sign, cudaStream_t s);
+
+// out[rows][F] = silu(gu[:, :F]) * gu[:, F:]
+cudaError_t swiglu_forward(const void* gu, void* out, int rows, int f, cudaStream_t s);
+// dgu[:, :F] = dout * up * dsilu(gate), dgu[:, F:] = dout * silu(gate)
+cudaError_t swiglu_backward(const void* dout, const void* gu, void* dgu, int rows, int f, cudaStream_t s);
+
+// Row-wise cross entropy over bf16 logits [rows][vocab] (row pitch `ld`): loss[row] = lse - logit[target], lse[row] saved.
+cudaError_t cross_entropy_forward(const void* logits, const int64_t* targets, float* loss, float* lse, int rows, int vocab,
+                                  long long ld, int64_t ignore_index, cudaStream_t s);
+// dlogits = (exp(logit - lse) - onehot) * gscale[0] * scale, written over `logits` (in place) or into `dlogits`.
+cudaError_t cross_entropy_backward(const void* logits, void* dlogits, const int64_t* targets, const float* lse,
+                                   const float* gscale, float scale, int rows, int vocab, long long ld, int64_t ignore_index,
+                                   cudaStream_t s);
+
+// out[row] = table[ids[row]]
+cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s);
+// dtable[ids[row]] += dout[row]   (fp32 or bf16 table gradient; atomics)
+cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim,
+                               cudaStream_t s);
+
+// Fused AdamW over flat buffers: bf16 params, fp32 master/m/v, grads bf16 or fp32.
+//   g' = g * grad_scale; m = b1 m + (1-b1) g'; v = b2 v + (1-b2) g'^2
+//   master = master * (1 - lr*wd) - lr * (m / bc1) / (sqrt(v / bc2) + eps); p = bf16(master)
+cudaError_t adamw_step(void* p_bf16, const void* grad, bool grad_f32, float* master, float* m, float* v, long long n,
+                       float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                       float grad_scale, cudaStream_t s);
+
+// y = a * x (16-bit, in place allowed) — used for gradient scaling of flat buffers.
+cudaError_t scale_bf16(void* x, long long n, float a, cudaStream_t s);
+
+}  // namespace elfb

@@ -1,0 +1,61 @@
+"""Locate and load the compiled extension (``elf_b200/csrc/_build/elf_b200_C.so``)."""
+
+from __future__ import annotations
+
+import importlib.util
+import sys
+from pathlib import Path
+
+import torch
+
+_BUILD_DIR = Path(__file__).resolve().parent.parent / "csrc" / "_build"
+_NAME = "elf_b200_C"
+_module = None
+_load_error: Exception | None = None
+
+
+def _try_load():
+    global _module, _load_error
+    if _module is not None or _load_error is not None:
+        return
+    so = _BUILD_DIR / f"{_NAME}.so"
+    if not so.exists():
+        _load_error = FileNotFoundError(f"{so} not found; run `python -m elf_b200.csrc.build`")
+        return
+    try:
+        spec = importlib.util.spec_from_file_location(_NAME, so)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        sys.modules[_NAME] = mod
+        _module = mod
+    except Exception as exc:  # missing libcuda on a CPU box, ABI mismatch, ...
+        _load_error = exc
+
+
+def available() -> bool:
+    """True when the extension is loaded (it loads on CPU-only machines too; its CUDA
+    entry points need a device, its host runtime does not)."""
+    _try_load()
+    return _module is not None
+
+
+def get():
+    """The extension module; raises with the reason when it cannot be loaded."""
+    _try_load()
+    if _module is None:
+        raise RuntimeError(f"elf_b200 native extension unavailable: {_load_error}")
+    return _module
+
+
+def cuda_ready() -> bool:
+    return torch.cuda.is_available() and available()
+
+
+def require_on_gpu() -> None:
+    """Called by ops before they would fall back to torch: on a machine with a GPU a
+    missing extension is an error, not a reason to run slowly."""
+    if torch.cuda.is_available() and not available():
+        raise RuntimeError(
+            f"a CUDA device is present but the elf_b200 extension is not loaded ({_load_error}); "
+            "build it with `python -m elf_b200.csrc.build`"
+        )

@@ -1,0 +1,424 @@
+"""The static schedule zoo.
+
+Every generator has the signature ``(placement, n_micro_batches) -> List[Operation]`` and
+returns the programs of **all** ranks, rank after rank (reference
+``elf/scheduling/schedulers.py``; registry keys in ``elf/scheduling/__init__.py:11-66``).
+
+Two construction styles are used:
+
+* closed forms for the schedules whose per-rank program is a simple function of the
+  rank's depth in the pipeline (GPipe, linear 1F1B, ZB-H1, ZB-H2, full-remat, inference);
+* a policy-driven **list scheduler** (``_list_schedule``) that plays the pipeline forward
+  in unit time steps and lets every idle rank pick its next op by priority
+  (backward-inputs > forward under an in-flight cap > backward-params).  It produces
+  interleaved 1F1B, Hanayo (any number of waves) and ZB-V for *any* number of
+  micro-batches; the reference's ZB-V is a closed form valid only for
+  ``nmb == 2 * n_devices`` (``elf/scheduling/schedulers.py:284-393``).
+
+All generators work on the placement they are given with ranks taken relative to the
+smallest rank in it, so a data-parallel replica offset cannot change the schedule
+(the reference derives ``stages_per_device`` from ``max(placement)``,
+``elf/scheduling/schedulers.py:52-54``, which breaks for shifted placements).
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Callable, Dict, List, Optional, Sequence
+
+from .scheduling import Operation, OperationType, OpOptions
+
+logger = logging.getLogger("schedulers")
+
+__all__ = [
+    "generate_afab_schedule",
+    "generate_1f1b_schedule",
+    "generate_hanayo_schedule",
+    "generate_full_remat_schedule",
+    "generate_zbh1_schedule",
+    "generate_zbh2_schedule",
+    "generate_zbv_schedule",
+    "generate_inference_schedule",
+    "FixedSchedule",
+    "whole_stage_remat",
+]
+
+T = OperationType
+
+
+def whole_stage_remat(name, _module=None) -> bool:
+    """Remat strategy that checkpoints the stage as one unit (root module has name '')."""
+    return name == ""
+
+
+class _Programs:
+    """Collects the per-rank programs and adds the loss ops around the last stage."""
+
+    def __init__(self, placement: Sequence[int]):
+        self.placement = list(placement)
+        self.last = len(self.placement) - 1
+        self.by_rank: Dict[int, List[Operation]] = {r: [] for r in sorted(set(self.placement))}
+
+    def F(self, stage: int, mb: int, **opts) -> None:
+        rank = self.placement[stage]
+        prog = self.by_rank[rank]
+        prog.append(Operation(stage, mb, T.FORWARD, rank, **opts))
+        if stage == self.last:
+            prog.append(Operation(stage, mb, T.LOSS_FORWARD, rank, **opts))
+
+    def B(self, stage: int, mb: int, **opts) -> None:
+        rank = self.placement[stage]
+        prog = self.by_rank[rank]
+        if stage == self.last:
+            prog.append(Operation(stage, mb, T.LOSS_BACKWARD, rank, **opts))
+        prog.append(Operation(stage, mb, T.BACKWARD_INPUTS, rank, **opts))
+
+    def W(self, stage: int, mb: int, **opts) -> None:
+        rank = self.placement[stage]
+        self.by_rank[rank].append(Operation(stage, mb, T.BACKWARD_PARAMS, rank, **opts))
+
+    def BW(self, stage: int, mb: int, **opts) -> None:
+        self.B(stage, mb, **opts)
+        self.W(stage, mb, **opts)
+
+    def flat(self) -> List[Operation]:
+        return [op for rank in self.by_rank for op in self.by_rank[rank]]
+
+
+def _stages_by_rank(placement: Sequence[int]) -> Dict[int, List[int]]:
+    out: Dict[int, List[int]] = {}
+    for stage, rank in enumerate(placement):
+        out.setdefault(rank, []).append(stage)
+    return dict(sorted(out.items()))
+
+
+# ---------------------------------------------------------------------------------------
+# closed forms
+# ---------------------------------------------------------------------------------------
+
+
+def generate_afab_schedule(placement, n_micro_batches) -> List[Operation]:
+    """GPipe: all forwards, then all backwards (B immediately followed by its W)."""
+    out = _Programs(placement)
+    for stages in _stages_by_rank(placement).values():
+        for mb in range(n_micro_batches):
+            for s in stages:
+                out.F(s, mb)
+        for mb in range(n_micro_batches):
+            for s in reversed(stages):
+                out.BW(s, mb)
+    return out.flat()
+
+
+def _is_linear(placement) -> bool:
+    return len(set(placement)) == len(placement)
+
+
+def generate_1f1b_schedule(placement, n_micro_batches) -> List[Operation]:
+    """One-forward-one-backward.  One stage per rank: the classic PipeDream-flush program
+    (``depth`` warm-up forwards, then B/W and F alternate, then the remaining B/W).
+    Several stages per rank (``[0..p-1] * v``): interleaved 1F1B with ``(p-d-1) + (v-1)p``
+    warm-up forwards at pipeline depth ``d`` when ``nmb`` is a multiple of ``p``; other
+    shapes come from the list scheduler under the same in-flight bound."""
+    n = n_micro_batches
+    if _is_linear(placement):
+        out = _Programs(placement)
+        n_stages = len(placement)
+        for s in range(n_stages):
+            warm = min(n, n_stages - s)
+            for mb in range(warm):
+                out.F(s, mb)
+            for i in range(n - warm):
+                out.BW(s, i)
+                out.F(s, warm + i)
+            for mb in range(n - warm, n):
+                out.BW(s, mb)
+        return out.flat()
+
+    ranks = sorted(set(placement))
+    p = len(ranks)
+    v = len(placement) // p
+    by_rank = _stages_by_rank(placement)
+    regular = n % p == 0 and all(len(st) == v for st in by_rank.values())
+    if not regular:
+        cap = {r: (p - d - 1) + (v - 1) * p + 1 for d, r in enumerate(ranks)}
+        return _list_schedule(placement, n, split_w=False, cap=cap)
+
+    # Virtual step k of a rank works on chunk (k // p) % v for forwards (mirrored for
+    # backwards) and on micro-batch p * (k // (p v)) + k % p: groups of p micro-batches
+    # sweep the chunks in turn.
+    def fwd_step(k):
+        return (k // p) % v, (k // (p * v)) * p + k % p
+
+    def bwd_step(k):
+        return v - 1 - (k // p) % v, (k // (p * v)) * p + k % p
+
+    out = _Programs(placement)
+    total = n * v
+    for d, r in enumerate(ranks):
+        stages = by_rank[r]
+        warm = min(total, (p - d - 1) + (v - 1) * p)
+        for k in range(warm):
+            c, mb = fwd_step(k)
+            out.F(stages[c], mb)
+        for i in range(total - warm):
+            c, mb = fwd_step(warm + i)
+            out.F(stages[c], mb)
+            c, mb = bwd_step(i)
+            out.BW(stages[c], mb)
+        for i in range(total - warm, total):
+            c, mb = bwd_step(i)
+            out.BW(stages[c], mb)
+    return out.flat()
+
+
+def generate_full_remat_schedule(placement, n_micro_batches) -> List[Operation]:
+    """Every rank but the last runs GPipe with the whole stage checkpointed in F; the last
+    rank runs F,B,W per micro-batch and keeps its activations."""
+    out = _Programs(placement)
+    by_rank = _stages_by_rank(placement)
+    last_rank = max(by_rank)
+    for rank, stages in by_rank.items():
+        if rank == last_rank:
+            for mb in range(n_micro_batches):
+                for s in stages:
+                    out.F(s, mb)
+                for s in reversed(stages):
+                    out.BW(s, mb)
+            continue
+        for mb in range(n_micro_batches):
+            for s in stages:
+                out.F(s, mb, **{OpOptions.REMAT_STRATEGY: whole_stage_remat})
+        for mb in range(n_micro_batches):
+            for s in reversed(stages):
+                out.BW(s, mb)
+    return out.flat()
+
+
+def _zero_bubble_linear(placement, n, warm_of: Callable[[int, int], int], lag_of: Callable[[int, int, int], int]):
+    """Shared shape of ZB-H1/ZB-H2 on a linear placement: ``warm`` forwards, one B, ``lag``
+    rounds of (F, B) with no W, then rounds of (W, F, B) until everything is issued."""
+    out = _Programs(placement)
+    p = len(set(placement))
+    for s in range(len(placement)):
+        warm = warm_of(p, s)
+        warm = min(n, warm)
+        f = b = w = 0
+        for _ in range(warm):
+            out.F(s, f)
+            f += 1
+        out.B(s, b)
+        b += 1
+        for _ in range(lag_of(p, s, warm)):
+            if f < n:
+                out.F(s, f)
+                f += 1
+            if b < n:
+                out.B(s, b)
+                b += 1
+        while f < n or b < n or w < n:
+            if w < n:
+                out.W(s, w)
+                w += 1
+            if f < n:
+                out.F(s, f)
+                f += 1
+            if b < n:
+                out.B(s, b)
+                b += 1
+    return out.flat()
+
+
+def generate_zbh1_schedule(placement, n_micro_batches) -> List[Operation]:
+    """ZB-H1: 1F1B's memory, W deferred by ``depth + 1`` backward slots.  The lag is the
+    stage's depth in the pipeline (the reference uses the *global* rank,
+    ``elf/scheduling/schedulers.py:223``, so replicas would disagree)."""
+    return _zero_bubble_linear(placement, n_micro_batches, lambda p, s: p - s, lambda p, s, warm: s)
+
+
+def generate_zbh2_schedule(placement, n_micro_batches) -> List[Operation]:
+    """ZB-H2: ``2(p - s) - 1`` warm-up forwards; every W is pushed behind the 1F1B body
+    so the tail bubble is filled with weight-gradient work."""
+    n = n_micro_batches
+    return _zero_bubble_linear(placement, n, lambda p, s: 2 * (p - s) - 1, lambda p, s, warm: max(0, n - 1 - warm))
+
+
+def generate_inference_schedule(placement, n_micro_batches) -> List[Operation]:
+    """Forward only; no loss ops."""
+    sched = []
+    for stage, rank in enumerate(placement):
+        for mb in range(n_micro_batches):
+            sched.append(Operation(stage, mb, T.FORWARD, rank))
+    sched.sort(key=lambda op: op.rank)  # stable: rank after rank
+    return sched
+
+
+class FixedSchedule:
+    """Replay ``{"order": [(kind, block_id, mb_id), ...]}`` with ``kind`` in ``f``/``b``/``w``
+    (tuple order as emitted by the ILP and read by the reference,
+    ``elf/scheduling/schedulers.py:408-440``)."""
+
+    def __init__(self, schedule_dict):
+        self.schedule_dict = schedule_dict
+
+    def __call__(self, placement, n_micro_batches) -> List[Operation]:
+        out = _Programs(placement)
+        emit = {"f": out.F, "b": out.B, "w": out.W}
+        for kind, block_id, mb_id in self.schedule_dict["order"]:
+            emit[str(kind).lower()](int(block_id), int(mb_id))
+        return out.flat()
+
+
+# ---------------------------------------------------------------------------------------
+# list scheduler
+# ---------------------------------------------------------------------------------------
+
+
+def _list_schedule(
+    placement,
+    n: int,
+    *,
+    split_w: bool,
+    cap: Dict[int, int] | int | None = None,
+    cost_f: int = 1,
+    cost_b: int = 1,
+    cost_w: int = 1,
+    hop: int = 0,
+) -> List[Operation]:
+    """Greedy unit-time simulation of the whole pipeline.
+
+    At every tick each idle rank starts, in this order of preference,
+    (1) the oldest ready backward-inputs (ready = own forward done and the next stage's B
+        done, ``hop`` ticks earlier when that stage is on another rank);
+    (2) the deepest ready forward, if the rank holds fewer than ``cap`` live
+        (stage, micro-batch) activations (live = forwarded, W not yet run);
+    (3) the oldest pending backward-params (only when ``split_w``; otherwise W is glued
+        to its B).
+    If the cap ever starves the whole pipeline it is lifted by one on the blocked ranks.
+    Because the result is read off a feasible timeline, the per-rank programs admit a
+    global order and cannot deadlock once comms are added.
+    """
+    n_stages = len(placement)
+    by_rank = _stages_by_rank(placement)
+    ranks = list(by_rank)
+    if cap is None:
+        cap = {r: n_stages * n for r in ranks}
+    elif isinstance(cap, int):
+        cap = {r: cap for r in ranks}
+    cap = dict(cap)
+
+    UNSET = -1
+    f_end = [[UNSET] * n for _ in range(n_stages)]
+    b_end = [[UNSET] * n for _ in range(n_stages)]
+    f_next = [0] * n_stages
+    b_next = [0] * n_stages
+    w_next = [0] * n_stages
+    busy_until = {r: 0 for r in ranks}
+    out = _Programs(placement)
+    total = n_stages * n * 3
+    done = 0
+    t = 0
+    idle_ticks = 0
+
+    def arrival(end: int, src_stage: int, dst_stage: int) -> int:
+        return end + (hop if placement[src_stage] != placement[dst_stage] else 0)
+
+    def f_ready(s: int) -> bool:
+        mb = f_next[s]
+        if mb >= n:
+            return False
+        if s == 0:
+            return True
+        e = f_end[s - 1][mb]
+        return e != UNSET and arrival(e, s - 1, s) <= t
+
+    def b_ready(s: int) -> bool:
+        mb = b_next[s]
+        if mb >= n or f_end[s][mb] == UNSET or f_end[s][mb] > t:
+            return False
+        if s == n_stages - 1:
+            return True
+        e = b_end[s + 1][mb]
+        return e != UNSET and arrival(e, s + 1, s) <= t
+
+    def live(rank: int) -> int:
+        return sum(f_next[s] - w_next[s] for s in by_rank[rank])
+
+    while done < total:
+        progressed = False
+        blocked_by_cap = []
+        for r in ranks:
+            if busy_until[r] > t:
+                progressed = True
+                continue
+            stages = by_rank[r]
+            cand_b = [s for s in stages if b_ready(s)]
+            if cand_b:
+                s = min(cand_b, key=lambda s: (b_next[s], s))
+                mb = b_next[s]
+                out.B(s, mb)
+                b_next[s] += 1
+                dur = cost_b
+                done += 1
+                if not split_w:
+                    out.W(s, mb)
+                    w_next[s] += 1
+                    dur += cost_w
+                    done += 1
+                b_end[s][mb] = t + cost_b
+                busy_until[r] = t + dur
+                progressed = True
+                continue
+            cand_f = [s for s in stages if f_ready(s)]
+            if cand_f:
+                if live(r) < cap[r]:
+                    s = max(cand_f, key=lambda s: (s, -f_next[s]))
+                    mb = f_next[s]
+                    out.F(s, mb)
+                    f_next[s] += 1
+                    f_end[s][mb] = t + cost_f
+                    busy_until[r] = t + cost_f
+                    done += 1
+                    progressed = True
+                    continue
+                blocked_by_cap.append(r)
+            if split_w:
+                cand_w = [s for s in stages if w_next[s] < b_next[s]]
+                if cand_w:
+                    s = min(cand_w, key=lambda s: (w_next[s], s))
+                    out.W(s, w_next[s])
+                    w_next[s] += 1
+                    busy_until[r] = t + cost_w
+                    done += 1
+                    progressed = True
+                    continue
+        if progressed:
+            idle_ticks = 0
+        else:
+            idle_ticks += 1
+            if idle_ticks > hop + 1:
+                if not blocked_by_cap:
+                    raise RuntimeError("list scheduler stalled: placement admits no feasible order")
+                for r in blocked_by_cap:
+                    cap[r] += 1
+                idle_ticks = 0
+        t += 1
+    return out.flat()
+
+
+def generate_hanayo_schedule(placement, n_micro_batches) -> List[Operation]:
+    """Hanayo wave schedule on ``[0..p-1, p-1..0] * waves``: forwards and (B, W) pairs are
+    interleaved across the legs of each wave; every rank keeps at most ``p`` live
+    micro-batches per local stage."""
+    p = len(set(placement))
+    return _list_schedule(placement, n_micro_batches, split_w=False, cap=max(1, len(placement) // p) * p)
+
+
+def generate_zbv_schedule(placement, n_micro_batches, *, cap: Optional[int] = None) -> List[Operation]:
+    """ZB-V on the V placement ``[0..p-1, p-1..0]`` for any number of micro-batches.  Each
+    rank holds at most ``2p`` live (stage, micro-batch) activations — the footprint of
+    1F1B — and weight-gradient passes fill what would otherwise be bubbles."""
+    p = len(set(placement))
+    if len(placement) != 2 * p:
+        logger.warning("zbv expects a V placement with two stages per rank, got %s", list(placement))
+    return _list_schedule(placement, n_micro_batches, split_w=True, cap=cap if cap is not None else 2 * p)
