@@ -1,0 +1,199 @@
+"""Point-to-point channels between pipeline stages.
+
+One ``Channel`` object exists per (producer block, consumer block, direction) and per end.
+Traffic on a channel is a FIFO of micro-batch tensors of one fixed shape, so the two ends
+always agree on ordering.  Transport:
+
+* NCCL: every channel owns a 2-rank process group (its own communicator and stream), so a
+  forward activation and a backward gradient between the same two GPUs never queue behind
+  each other — the same reason the reference builds ``group_fwd``/``group_bwd`` per block
+  pair (``elf/pipeline.py:640-723``).  Groups are derived from the placement and the
+  signatures, which every rank already knows, so no ``all_gather_object`` round is needed
+  and each group is created exactly once.
+* gloo (CPU): the pipeline group with a per-(channel, micro-batch) tag.
+
+Shape/dtype are learned by the receiving end from a one-off int64 header message that
+precedes the first payload (the reference sends 16 floats with a blocking ``recv``,
+``elf/execution/block.py:529-570``).  The header is received with ``irecv`` and only waited
+for when the consumer actually needs the tensor, so posting a recv early can never block
+the host on a peer that has not reached its send yet.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..utils.metadata import TensorMetadata
+
+__all__ = ["Channel", "ChannelTable", "edge_list"]
+
+
+def edge_list(signatures) -> List[Tuple[int, int]]:
+    """All (producer block, consumer block) pairs, sorted."""
+    edges = set()
+    for dst, sig in enumerate(signatures):
+        for src in sig.get_all_sources():
+            if src is not None:
+                edges.add((src, dst))
+    for src, sig in enumerate(signatures):
+        for dst in sig.get_all_targets():
+            if dst is not None:
+                edges.add((src, dst))
+    return sorted(edges)
+
+
+class _Pending:
+    __slots__ = ("work", "tensor", "mb")
+
+    def __init__(self, mb, work=None, tensor=None):
+        self.mb, self.work, self.tensor = mb, work, tensor
+
+
+class Channel:
+    """One end of one directed stream of same-shaped tensors."""
+
+    def __init__(self, src_block: int, dst_block: int, direction: str, peer_global_rank: int, group, device, index: int, n_channels: int):
+        self.src_block, self.dst_block, self.direction = src_block, dst_block, direction
+        self.peer = peer_global_rank
+        self.group = group
+        self.device = device
+        self.index = index
+        self.n_channels = max(1, n_channels)
+        self.metadata: Optional[TensorMetadata] = None
+        self.header_sent = False
+        self._header_work = None
+        self._header_buf: Optional[torch.Tensor] = None
+        self._deferred: List[Tuple[int, int]] = []  # (mb, batch) recvs posted before the shape was known
+        self._posted: Dict[int, _Pending] = {}
+        self._sends: List = []
+        self._tagged = dist.get_backend(group) != "nccl"
+
+    def _tag(self, mb: int, header: bool = False) -> int:
+        if not self._tagged:
+            return 0
+        return 1 + ((0 if header else mb + 1) * self.n_channels + self.index)
+
+    # ------------------------------------------------------------------ sending
+    def send(self, tensor: torch.Tensor, mb: int) -> None:
+        payload = tensor.detach()
+        if payload.device != self.device:
+            payload = payload.to(self.device)
+        payload = payload.contiguous()
+        if not self.header_sent:
+            self.header_sent = True
+            head = TensorMetadata(shape=list(payload.shape[1:]), dtype=payload.dtype).to_tensor(self.device)
+            self._sends.append((dist.isend(head, dst=self.peer, group=self.group, tag=self._tag(mb, True)), head))
+        self._sends.append((dist.isend(payload, dst=self.peer, group=self.group, tag=self._tag(mb)), payload))
+        if len(self._sends) > 64:
+            self.reap_sends()
+
+    def reap_sends(self, block: bool = False) -> None:
+        """Drop handles of completed sends (the handle keeps the payload alive until then)."""
+        keep = []
+        for work, t in self._sends:
+            if block:
+                work.wait()
+            elif not work.is_completed():
+                keep.append((work, t))
+        self._sends = keep
+
+    # ------------------------------------------------------------------ receiving
+    def set_metadata(self, meta: TensorMetadata) -> None:
+        """Tell the receiving end the shape without a header (used for backward channels,
+        whose payload has the shape of a tensor this rank produced itself)."""
+        self.metadata = meta
+        self.header_sent = True
+
+    def post_recv(self, mb: int, batch: int) -> None:
+        if self.metadata is None:
+            if self._header_work is None:
+                self._header_buf = torch.zeros(TensorMetadata.MAX_SIZE, dtype=torch.int64, device=self.device)
+                self._header_work = dist.irecv(self._header_buf, src=self.peer, group=self.group, tag=self._tag(mb, True))
+            self._deferred.append((mb, batch))
+            return
+        self._post(mb, batch)
+
+    def _post(self, mb: int, batch: int) -> None:
+        buf = torch.empty((batch, *self.metadata.shape), dtype=self.metadata.dtype, device=self.device)
+        work = dist.irecv(buf, src=self.peer, group=self.group, tag=self._tag(mb))
+        self._posted[mb] = _Pending(mb, work, buf)
+
+    def _resolve_header(self) -> None:
+        if self.metadata is None:
+            self._header_work.wait()
+            self.metadata = TensorMetadata.from_tensor(self._header_buf.cpu(), device=self.device)
+            self._header_work = self._header_buf = None
+        for mb, batch in self._deferred:
+            self._post(mb, batch)
+        self._deferred.clear()
+
+    def wait(self, mb: int) -> torch.Tensor:
+        if mb not in self._posted:
+            if not any(m == mb for m, _ in self._deferred):
+                raise KeyError(f"no recv posted for micro-batch {mb} on channel {self}")
+            self._resolve_header()
+        pending = self._posted.pop(mb)
+        pending.work.wait()
+        return pending.tensor
+
+    def reset(self) -> None:
+        self.reap_sends(block=True)
+        self._posted.clear()
+        self._deferred.clear()
+
+    def __repr__(self) -> str:
+        return f"Channel({self.src_block}->{self.dst_block} {self.direction}, peer={self.peer})"
+
+
+class ChannelTable:
+    """All channels touching this rank, keyed by ``(src_block, dst_block, direction)``
+    where ``src_block`` is the block the *payload* comes from."""
+
+    def __init__(self, placement, signatures, local_rank: int, pp_group, device, *, pp: int, dp: int = 1, dp_rank: int = 0, timeout=None, dedicated_groups: Optional[bool] = None):
+        """``placement`` holds pipeline-local ranks; global rank = ``replica * pp + local``.
+        With dedicated groups, every process of the job must construct its table at the
+        same time (``new_group`` is collective over the world), replicas included."""
+        self.channels: Dict[Tuple[int, int, str], Channel] = {}
+        self._groups = []
+        backend = dist.get_backend(pp_group)
+        if dedicated_groups is None:
+            dedicated_groups = backend == "nccl"
+        edges = [(a, b) for a, b in edge_list(signatures) if placement[a] != placement[b]]
+        n = 2 * len(edges)
+        for replica in range(dp if dedicated_groups else 1):
+            if not dedicated_groups:
+                replica = dp_rank
+            offset = replica * pp
+            for i, (a, b) in enumerate(edges):
+                ra, rb = placement[a], placement[b]
+                mine = replica == dp_rank and local_rank in (ra, rb)
+                for j, direction in enumerate(("fwd", "bwd")):
+                    group = pp_group
+                    if dedicated_groups:
+                        kwargs = {"timeout": timeout} if timeout is not None else {}
+                        group = dist.new_group(sorted({offset + ra, offset + rb}), backend=backend, **kwargs)
+                        if mine:
+                            self._groups.append(group)
+                    if not mine:
+                        continue
+                    src, dst = (a, b) if direction == "fwd" else (b, a)
+                    peer_local = rb if local_rank == ra else ra
+                    self.channels[(src, dst, direction)] = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
+
+    def get(self, src_block: int, dst_block: int, direction: str) -> Channel:
+        return self.channels[(src_block, dst_block, direction)]
+
+    def reset(self) -> None:
+        for ch in self.channels.values():
+            ch.reset()
+
+    def destroy(self) -> None:
+        for g in self._groups:
+            try:
+                dist.destroy_process_group(g)
+            except Exception:
+                pass
+        self._groups.clear()
