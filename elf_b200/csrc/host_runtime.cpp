@@ -127,7 +127,13 @@ class PinnedArena {
 
 }  // namespace
 
+// uint8 CPU tensor over arena memory; the arena, not the tensor, owns the bytes.
+static at::Tensor host_tensor(uintptr_t addr, int64_t nbytes) {
+  return at::from_blob(reinterpret_cast<void*>(addr), {nbytes}, at::TensorOptions().dtype(at::kByte).device(at::kCPU));
+}
+
 void register_host_runtime(pybind11::module_& m) {
+  m.def("host_tensor", &host_tensor, "view arena memory as a uint8 CPU tensor");
   py::class_<PinnedArena>(m, "PinnedArena")
       .def(py::init<size_t>(), py::arg("min_block_bytes") = size_t(64) << 20)
       .def("reserve", &PinnedArena::reserve)

@@ -149,25 +149,31 @@ class Channel:
 
 
 class ChannelTable:
-    """All channels touching this rank, keyed by ``(src_block, dst_block, direction)``
-    where ``src_block`` is the block the *payload* comes from."""
+    """All channels touching this rank, keyed by ``(src_block, dst_block, direction, k)``
+    where ``src_block`` is the block the *payload* comes from and ``k`` numbers the tensors
+    exchanged by that pair of blocks."""
 
     def __init__(self, placement, signatures, local_rank: int, pp_group, device, *, pp: int, dp: int = 1, dp_rank: int = 0, timeout=None, dedicated_groups: Optional[bool] = None):
         """``placement`` holds pipeline-local ranks; global rank = ``replica * pp + local``.
         With dedicated groups, every process of the job must construct its table at the
         same time (``new_group`` is collective over the world), replicas included."""
-        self.channels: Dict[Tuple[int, int, str], Channel] = {}
+        self.channels: Dict[Tuple[int, int, str, int], Channel] = {}
         self._groups = []
         backend = dist.get_backend(pp_group)
         if dedicated_groups is None:
             dedicated_groups = backend == "nccl"
-        edges = [(a, b) for a, b in edge_list(signatures) if placement[a] != placement[b]]
+        # one channel per tensor crossing the edge: a channel carries one fixed shape
+        edges = []
+        for a, b in edge_list(signatures):
+            if placement[a] != placement[b]:
+                width = max(1, sum(1 for src in signatures[b].sources if src == a))
+                edges += [(a, b, k) for k in range(width)]
         n = 2 * len(edges)
         for replica in range(dp if dedicated_groups else 1):
             if not dedicated_groups:
                 replica = dp_rank
             offset = replica * pp
-            for i, (a, b) in enumerate(edges):
+            for i, (a, b, k) in enumerate(edges):
                 ra, rb = placement[a], placement[b]
                 mine = replica == dp_rank and local_rank in (ra, rb)
                 for j, direction in enumerate(("fwd", "bwd")):
@@ -181,10 +187,11 @@ class ChannelTable:
                         continue
                     src, dst = (a, b) if direction == "fwd" else (b, a)
                     peer_local = rb if local_rank == ra else ra
-                    self.channels[(src, dst, direction)] = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
+                    self.channels[(src, dst, direction, k)] = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
 
-    def get(self, src_block: int, dst_block: int, direction: str) -> Channel:
-        return self.channels[(src_block, dst_block, direction)]
+    def get(self, src_block: int, dst_block: int, direction: str, k: int = 0) -> Channel:
+        """Channel of the ``k``-th tensor that ``src_block`` sends to ``dst_block``."""
+        return self.channels[(src_block, dst_block, direction, k)]
 
     def reset(self) -> None:
         for ch in self.channels.values():

@@ -1,0 +1,108 @@
+"""End-to-end numerics of the runtime on CPU/gloo ranks against the non-pipelined model."""
+
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_ranks
+
+pytestmark = pytest.mark.dist
+
+ATOL = RTOL = 1e-3
+
+
+def _reference(model, ids, targets, lr=1e-3):
+    ref = copy.deepcopy(model)
+    loss = ref.loss_fn(ref(ids), targets)
+    loss.backward()
+    grads = {n: p.grad.clone() for n, p in ref.named_parameters()}
+    opt = torch.optim.AdamW(ref.parameters(), lr=lr)
+    opt.step()
+    return loss.detach(), grads, {n: p.detach().clone() for n, p in ref.named_parameters()}
+
+
+def _stage_param_names(model, n_stages):
+    """Map (stage, local name) -> global name for the flat sequential split."""
+    from elf_b200.models.gpt import gpt_stages
+
+    names = {}
+    idx = 0
+    for s, stage in enumerate(gpt_stages(model, n_stages)):
+        for local_idx, layer in enumerate(stage.children()):
+            for n, _ in layer.named_parameters():
+                names[(s, f"{local_idx}.{n}")] = f"{idx}.{n}"
+            idx += 1
+    return names
+
+
+def _worker(rank, world, scheduler, placement, dp, nmb, split_w):
+    from elf_b200 import Pipeline, replace_layer_with_layer_dw
+    from elf_b200.models.gpt import GPT, GPTConfig, gpt_stages
+
+    torch.manual_seed(0)
+    cfg = GPTConfig()
+    model = GPT(cfg)
+    pp = world // dp
+    batch = 8
+    g = torch.Generator().manual_seed(0)
+    ids_all = torch.randint(0, cfg.vocab, (dp * batch, cfg.seq_len + 1), generator=g)
+    ids, targets = ids_all[:, :-1].contiguous(), ids_all[:, 1:].contiguous()
+    ref_loss, ref_grads, ref_params = _reference(model, ids, targets)
+
+    n_stages = len(placement)
+    stages = gpt_stages(copy.deepcopy(model), n_stages)
+    names = _stage_param_names(model, n_stages)
+    pp_rank, dp_rank = rank % pp, rank // pp
+    mine = [s for s in range(n_stages) if placement[s] == pp_rank]
+    parts = [stages[s] for s in mine]
+    if split_w:
+        for p in parts:
+            replace_layer_with_layer_dw(p)
+    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=placement, dp=dp, outputs="device")
+    my_ids = ids[dp_rank * batch : (dp_rank + 1) * batch]
+    my_tgt = targets[dp_rank * batch : (dp_rank + 1) * batch]
+    out, loss = pipe(my_ids, my_tgt, GPT.loss_fn, split_size=batch // nmb)
+    if pipe.is_last():
+        assert loss is not None
+        torch.testing.assert_close(loss, ref_loss, atol=ATOL, rtol=RTOL)
+        assert len(out) == nmb
+    else:
+        assert out is None and loss is None
+    for block in pipe.blocks:
+        for n, p in block.model.named_parameters():
+            gname = names[(block.id, n)]
+            assert p.grad is not None, gname
+            torch.testing.assert_close(p.grad, ref_grads[gname], atol=ATOL, rtol=RTOL, msg=lambda m: f"{gname}: {m}")
+    opt = torch.optim.AdamW(list(pipe.parameters()), lr=1e-3)
+    opt.step()
+    for block in pipe.blocks:
+        for n, p in block.model.named_parameters():
+            torch.testing.assert_close(p.detach(), ref_params[names[(block.id, n)]], atol=ATOL, rtol=RTOL)
+    # a second step reuses the cached schedule and accumulates on top of zeroed grads
+    pipe.zero_grad()
+    pipe(my_ids, my_tgt, GPT.loss_fn, split_size=batch // nmb)
+    pipe.clear()
+
+
+@pytest.mark.parametrize(
+    "scheduler,placement,dp,nmb,split_w",
+    [
+        ("1f1b", [0, 1], 1, 4, False),  # the plumbing config: pp=2, 1F1B, 4 micro-batches
+        ("afab", [0, 1], 1, 4, False),
+        ("zbh1", [0, 1], 1, 4, True),
+        ("zbh2", [0, 1], 1, 4, True),
+        ("zbv", [0, 1, 1, 0], 1, 4, True),
+        ("hanayo", [0, 1, 1, 0], 1, 4, False),
+        ("1f1b", [0, 1, 0, 1], 1, 4, False),
+        ("full_remat", [0, 1], 1, 4, False),
+    ],
+)
+def test_pipeline_matches_single_process(scheduler, placement, dp, nmb, split_w):
+    run_ranks(_worker, len(set(placement)) * dp, scheduler, placement, dp, nmb, split_w)
+
+
+@pytest.mark.parametrize("scheduler,placement", [("1f1b", [0, 1]), ("zbv", [0, 1, 1, 0]), ("zbh1", [0, 1]), ("hanayo", [0, 1, 1, 0])])
+def test_data_parallel_replicas(scheduler, placement):
+    run_ranks(_worker, 4, scheduler, placement, 2, 4, scheduler.startswith("zb"))
