@@ -39,12 +39,60 @@ def available() -> bool:
     return _module is not None
 
 
+# Kernel launches per Python-visible entry point (a `gemm` call is one launch,
+# `rmsnorm_bwd` two, ...), kept so that benchmarks can report how many of this package's
+# kernels ran inside a timed region.
+_LAUNCHES_PER_CALL = {
+    "gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 2, "rope_": 1, "swiglu_fwd": 1, "swiglu_bwd": 1, "ce_fwd": 1,
+    "ce_bwd": 1, "embedding_fwd": 1, "embedding_bwd": 1, "adamw": 1, "scale_": 1, "attention_fwd": 1,
+    "attention_bwd": 3, "push_reduce": 1, "gemm_dw_reduce": 1,
+}
+launch_count = 0
+
+
+class _Counting:
+    """Attribute proxy over the extension module that counts kernel launches."""
+
+    def __init__(self, mod):
+        object.__setattr__(self, "_mod", mod)
+        object.__setattr__(self, "_cache", {})
+
+    def __getattr__(self, name):
+        cached = self._cache.get(name)
+        if cached is not None:
+            return cached
+        fn = getattr(self._mod, name)
+        n = _LAUNCHES_PER_CALL.get(name)
+        if n is None or not callable(fn):
+            return fn
+
+        def counted(*args, __fn=fn, __n=n, **kwargs):
+            global launch_count
+            launch_count += __n
+            return __fn(*args, **kwargs)
+
+        self._cache[name] = counted
+        return counted
+
+
+_proxy = None
+
+
 def get():
-    """The extension module; raises with the reason when it cannot be loaded."""
+    """The extension module (behind a launch-counting proxy); raises with the reason when
+    it cannot be loaded."""
+    global _proxy
     _try_load()
     if _module is None:
         raise RuntimeError(f"elf_b200 native extension unavailable: {_load_error}")
-    return _module
+    if _proxy is None:
+        _proxy = _Counting(_module)
+    return _proxy
+
+
+def launches() -> int:
+    """Kernels of this package launched so far in this process."""
+    return launch_count
 
 
 def cuda_ready() -> bool:

@@ -1,0 +1,230 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from elf_b200.ops import _ext
+
+    assert _ext.available(), "the native extension must be built for GPU tests"
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (200, 264, 72), (1000, 520, 328), (4096, 1024, 2048), (96, 8, 8)])
+def test_gemm_family(dev, m, n, k):
+    from elf_b200.ops import gemm as G
+
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+    dy = torch.randn(m, n, device=dev, dtype=torch.bfloat16)
+    bias = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    assert rel_err(G.linear_forward(x, w, bias), x.float() @ w.float().t() + bias.float()) < 5e-3
+    assert rel_err(G.linear_forward(x, w), x.float() @ w.float().t()) < 5e-3
+    assert rel_err(G.linear_input_grad(dy, w), dy.float() @ w.float()) < 5e-3
+    ref_dw = dy.float().t() @ x.float()
+    assert rel_err(G.linear_weight_grad(dy, x), ref_dw) < 5e-3
+    acc32 = torch.full((n, k), 0.5, device=dev, dtype=torch.float32)
+    G.linear_weight_grad(dy, x, out=acc32)
+    assert rel_err(acc32, ref_dw + 0.5) < 1e-4
+    acc16 = torch.ones(n, k, device=dev, dtype=torch.bfloat16)
+    G.linear_weight_grad(dy, x, out=acc16)
+    assert rel_err(acc16, ref_dw + 1) < 5e-3
+    G.check_status()
+
+
+def test_gemm_fp16_and_strided(dev):
+    from elf_b200.ops import gemm as G
+
+    x = torch.randn(300, 512, device=dev, dtype=torch.float16)[:, :256]  # row pitch 512
+    w = torch.randn(128, 256, device=dev, dtype=torch.float16) * 0.05
+    assert rel_err(G.linear_forward(x, w), x.float() @ w.float().t()) < 2e-3
+    G.check_status()
+
+
+def test_linear_dw_layer_matches_autograd(dev):
+    from elf_b200.zb_utils import LinearDW
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(256, 512, bias=True, device=dev, dtype=torch.bfloat16)
+    ref = torch.nn.Linear(256, 512, bias=True, device=dev, dtype=torch.float32)
+    ref.load_state_dict({k: v.float() for k, v in lin.state_dict().items()})
+    dw = LinearDW(lin)
+    x = torch.randn(4, 96, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    xr = x.detach().float().requires_grad_()
+    y = dw(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref(xr).backward(g.float())
+    assert dw.weight.grad is None  # B pass leaves parameters alone
+    dw.move_last_computed("input", 0)
+    dw.move_last_computed("grad_output", 0)
+    dw.backward(0)
+    assert rel_err(y, ref(xr)) < 5e-3
+    assert rel_err(x.grad, xr.grad) < 5e-3
+    assert rel_err(dw.weight.grad, ref.weight.grad) < 5e-3
+    assert rel_err(dw.bias.grad, ref.bias.grad) < 5e-3
+
+
+@pytest.mark.parametrize("rows,dim", [(64, 256), (300, 4096), (17, 8192)])
+def test_rmsnorm(dev, rows, dim):
+    from elf_b200.ops import fused as Fu
+
+    torch.manual_seed(1)
+    x = torch.randn(rows, dim, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, dim, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(dim, device=dev)).to(torch.bfloat16).requires_grad_()
+    y = Fu.rms_norm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = F.rms_norm(xf, (dim,), wf, 1e-5)
+    yr.backward(g.float())
+    assert rel_err(y, yr) < 5e-3 and rel_err(x.grad, xf.grad) < 1e-2 and rel_err(w.grad, wf.grad) < 1e-2
+    # fused residual add + norm
+    x.grad = None
+    w.grad = None
+    y2, h = Fu.add_rms_norm(x, r, w, 1e-5)
+    gy, gh = torch.randn_like(y2), torch.randn_like(h)
+    torch.autograd.backward([y2, h], [gy, gh])
+    xf, rf, wf = x.detach().float().requires_grad_(), r.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    hr = (xf + rf).to(torch.bfloat16).float() + (xf + rf - (xf + rf).detach())  # same rounding of h as the kernel
+    yr = F.rms_norm(hr, (dim,), wf, 1e-5)
+    torch.autograd.backward([yr, hr], [gy.float(), gh.float()])
+    assert rel_err(h, hr) < 5e-3 and rel_err(y2, yr) < 5e-3
+    assert rel_err(x.grad, xf.grad) < 1e-2 and rel_err(r.grad, rf.grad) < 1e-2 and rel_err(w.grad, wf.grad) < 1e-2
+
+
+def test_rope(dev):
+    from elf_b200.ops import fused as Fu
+
+    b, s, hq, hkv, d = 2, 128, 4, 2, 128
+    cos, sin = Fu.rope_tables(s, d, 500000.0, dev)
+    x = torch.randn(b * s, (hq + 2 * hkv) * d, device=dev, dtype=torch.bfloat16)
+    ref = Fu._rope_ref(x.float(), cos, sin, hq + hkv, d, s, 1.0)
+    leaf = x.clone().requires_grad_()
+    out = Fu.rope_(leaf * 1, cos, sin, hq + hkv, d, s)
+    assert rel_err(out, ref) < 5e-3
+    g = torch.randn_like(out)
+    out.backward(g)
+    gref = Fu._rope_ref(g.float(), cos, sin, hq + hkv, d, s, -1.0)
+    assert rel_err(leaf.grad, gref) < 5e-3
+
+
+def test_swiglu(dev):
+    from elf_b200.ops import fused as Fu
+
+    gu = torch.randn(300, 2 * 1408, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    out = Fu.swiglu(gu)
+    g = torch.randn_like(out)
+    out.backward(g)
+    guf = gu.detach().float().requires_grad_()
+    a, b = guf.chunk(2, -1)
+    ref = F.silu(a) * b
+    ref.backward(g.float())
+    assert rel_err(out, ref) < 5e-3 and rel_err(gu.grad, guf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("rows,vocab", [(64, 1024), (33, 32000), (16, 128256)])
+def test_cross_entropy(dev, rows, vocab):
+    from elf_b200.ops import fused as Fu
+
+    torch.manual_seed(2)
+    logits = (torch.randn(rows, vocab, device=dev) * 2).to(torch.bfloat16)
+    tgt = torch.randint(0, vocab, (rows,), device=dev)
+    lf = logits.float().requires_grad_()
+    ref = F.cross_entropy(lf, tgt, reduction="sum")
+    (ref / 7).backward()
+    leaf = logits.clone().requires_grad_()
+    loss = Fu.cross_entropy(leaf, tgt, reduction="sum")
+    (loss / 7).backward()
+    assert abs(loss.item() - ref.item()) / abs(ref.item()) < 1e-3
+    assert rel_err(leaf.grad, lf.grad) < 1e-2
+
+
+def test_embedding(dev):
+    from elf_b200.ops import fused as Fu
+
+    table = torch.randn(1000, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (4, 77), device=dev)
+    out = Fu.embedding(table, ids)
+    assert torch.equal(out, F.embedding(ids, table))
+    g = torch.randn_like(out)
+    out.backward(g)
+    tf = table.detach().float().requires_grad_()
+    F.embedding(ids, tf).backward(g.float())
+    assert rel_err(table.grad, tf.grad) < 1e-2
+
+
+def test_fused_adamw(dev):
+    from elf_b200.optim import FusedAdamW
+
+    torch.manual_seed(3)
+    ps = [torch.nn.Parameter(torch.randn(257, 33, device=dev).to(torch.bfloat16)), torch.nn.Parameter(torch.randn(1001, device=dev).to(torch.bfloat16))]
+    ref = [torch.nn.Parameter(p.detach().float().clone()) for p in ps]
+    opt = FusedAdamW(ps, lr=1e-2, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1)
+    ropt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1)
+    for _ in range(4):
+        for p, q in zip(ps, ref):
+            g = torch.randn_like(p)
+            p.grad.copy_(g)
+            q.grad = g.float()
+        opt.step()
+        ropt.step()
+        opt.zero_grad()
+    for (w, q) in zip([opt.master[0]], [torch.cat([r.detach().reshape(-1) for r in ref])]):
+        got = torch.cat([w[o : o + p.numel()] for o, p in zip(opt.groups[0].offsets, ps)])
+        assert rel_err(got, q) < 1e-5
+    for p, q in zip(ps, ref):
+        assert rel_err(p, q) < 5e-3
+
+
+def test_llama_layer_matches_fp32_reference(dev):
+    """A decoder layer on the kernels vs. the same module in fp32 on torch ops."""
+    from elf_b200.models.llama import LlamaConfig, LlamaDecoderLayer, init_llama_
+    from elf_b200.ops import gemm
+    from elf_b200.zb_utils import LayerDW, replace_layer_with_layer_dw
+
+    cfg = LlamaConfig(n_layers=1, d_model=512, n_heads=4, n_kv_heads=2, ffn=1024, vocab=1024, seq_len=256)
+    torch.manual_seed(0)
+    layer = init_llama_(LlamaDecoderLayer(cfg).to(dev).to(torch.bfloat16), 0.05, seed=1)
+    ref = LlamaDecoderLayer(cfg).to(dev).float()
+    ref.load_state_dict({k: v.float() for k, v in layer.state_dict().items()})
+    replace_layer_with_layer_dw(layer)
+    x = torch.randn(2, 256, 512, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    xr = x.detach().float().requires_grad_()
+    y = layer(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    for m in layer.modules():
+        if isinstance(m, LayerDW):
+            m.move_last_computed("input", 0)
+            m.move_last_computed("grad_output", 0)
+            m.backward(0)
+    gemm.set_enabled(False)
+    try:
+        yr = ref(xr)
+        yr.backward(g.float())
+    finally:
+        gemm.set_enabled(True)
+    assert rel_err(y, yr) < 2e-2
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    for (n, p), (_, q) in zip(layer.named_parameters(), ref.named_parameters()):
+        assert rel_err(p.grad, q.grad) < 3e-2, n
+    gemm.check_status()
+
+
+def test_smoke_entry(dev):
+    import __graft_entry__
+
+    __graft_entry__.smoke()
