@@ -22,6 +22,8 @@
 // abort flag, all roles fall through to the common exit, TMEM is released and an error
 // code is written to `status`.
 
+#include <cstdio>
+
 #include "sm100_ptx.cuh"
 #include "gemm_sm100.h"
 
@@ -343,6 +345,13 @@ static EncodeFn get_encode_fn() {
 // box = (box_cols inner, box_rows outer), 128B swizzle, zero fill outside the matrix.
 const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t rows, uint64_t cols, uint64_t ld,
                          uint32_t box_cols, uint32_t box_rows) {
+  // Driver entry points need a CUDA context current on the calling thread; autograd runs
+  // backward passes on worker threads that may not have made a runtime call yet.
+  static thread_local bool context_ready = false;
+  if (!context_ready) {
+    cudaFree(nullptr);
+    context_ready = true;
+  }
   EncodeFn enc = get_encode_fn();
   if (!enc) return "cuTensorMapEncodeTiled entry point not found";
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return "TMA operand base address is not 16-byte aligned";
@@ -354,7 +363,11 @@ const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t ro
   CUresult r = enc(out, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+  if (r == CUDA_SUCCESS) return nullptr;
+  static thread_local char msg[256];
+  snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed (CUresult %d) for ptr=%p rows=%llu cols=%llu ld=%llu box=(%u,%u)", (int)r, ptr,
+           (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_cols, box_rows);
+  return msg;
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>

@@ -120,7 +120,9 @@ class LlamaDecoderLayer(nn.Module):
         b, s, d = x.shape
         hq, hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         cos, sin = self._tables(x.device, s)
-        qkv = self.wqkv(self.norm1(x)).view(b * s, (hq + 2 * hkv) * hd)
+        # the projection runs on a 2-D view so that its output is a base tensor RoPE may
+        # rotate in place
+        qkv = self.wqkv(self.norm1(x).view(b * s, d))
         qkv = _f.rope_(qkv, cos, sin, hq + hkv, hd, s).view(b, s, hq + 2 * hkv, hd)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq : hq + hkv], qkv[:, :, hq + hkv :]
         a = _attn.attention(q, k, v, causal=True).reshape(b, s, hq * hd)

@@ -127,7 +127,7 @@ class _Rope(torch.autograd.Function):
     def backward(ctx, g):
         cos, sin = ctx.saved_tensors
         n_rot_heads, head_dim, seq_len = ctx.geom
-        g = g.contiguous()
+        g = g.clone(memory_format=torch.contiguous_format)  # incoming gradients are not ours to overwrite
         _ext.get().rope_(g, cos, sin, n_rot_heads, head_dim, seq_len, True)
         return g, None, None, None, None, None
 

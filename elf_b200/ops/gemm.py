@@ -88,17 +88,19 @@ def _rows(t: torch.Tensor) -> torch.Tensor:
 
 def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     x2 = _rows(x)
-    y = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+    # allocated in its final shape: the result must not be a view made inside an autograd
+    # Function, or later in-place ops on it (RoPE) would be rejected
+    y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
     b = None if bias is None else bias.to(x.dtype).contiguous()
-    _ext.get().gemm(x2, _rows(w), y, b, False, False, False, 1.0, status(x.device))
-    return y.view(*x.shape[:-1], w.shape[0])
+    _ext.get().gemm(x2, _rows(w), y.view(-1, w.shape[0]), b, False, False, False, 1.0, status(x.device))
+    return y
 
 
 def linear_input_grad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     dy2 = _rows(dy)
-    dx = torch.empty((dy2.shape[0], w.shape[1]), dtype=dy.dtype, device=dy.device)
-    _ext.get().gemm(dy2, _rows(w), dx, None, False, True, False, 1.0, status(dy.device))
-    return dx.view(*dy.shape[:-1], w.shape[1])
+    dx = torch.empty((*dy.shape[:-1], w.shape[1]), dtype=dy.dtype, device=dy.device)
+    _ext.get().gemm(dy2, _rows(w), dx.view(-1, w.shape[1]), None, False, True, False, 1.0, status(dy.device))
+    return dx
 
 
 def linear_weight_grad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, alpha: float = 1.0, out_dtype=None) -> torch.Tensor:

@@ -98,7 +98,7 @@ def test_rmsnorm(dev, rows, dim):
     gy, gh = torch.randn_like(y2), torch.randn_like(h)
     torch.autograd.backward([y2, h], [gy, gh])
     xf, rf, wf = x.detach().float().requires_grad_(), r.detach().float().requires_grad_(), w.detach().float().requires_grad_()
-    hr = (xf + rf).to(torch.bfloat16).float() + (xf + rf - (xf + rf).detach())  # same rounding of h as the kernel
+    hr = (xf + rf).to(torch.bfloat16).float().detach() + (xf + rf - (xf + rf).detach())  # h rounded to bf16 as the kernel stores it
     yr = F.rms_norm(hr, (dim,), wf, 1e-5)
     torch.autograd.backward([yr, hr], [gy.float(), gh.float()])
     assert rel_err(h, hr) < 5e-3 and rel_err(y2, yr) < 5e-3
@@ -116,8 +116,8 @@ def test_rope(dev):
     out = Fu.rope_(leaf * 1, cos, sin, hq + hkv, d, s)
     assert rel_err(out, ref) < 5e-3
     g = torch.randn_like(out)
-    out.backward(g)
     gref = Fu._rope_ref(g.float(), cos, sin, hq + hkv, d, s, -1.0)
+    out.backward(g)
     assert rel_err(leaf.grad, gref) < 5e-3
 
 
