@@ -42,22 +42,62 @@ constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;  // rasterisation: tiles of GROUP_M consecutive M-blocks share B panels in L2
 constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
-struct TileCoord {
-  int m, n;
+// A work unit is a 128-row slab of BN/split columns.  Units [0, full_units) are whole
+// 128x256 tiles of the complete waves; the tiles of the last, partial wave are cut into
+// `split` column strips each (split = 1, 2 or 4) so that the tail keeps all SMs busy for a
+// fraction of a tile time instead of leaving most of them idle for a whole one.
+struct WorkUnit {
+  int m, n0, width;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
-  const int per_group = GROUP_M * tiles_n;
+struct Schedule {
+  int tiles_m, tiles_n, full_tiles, split, total_units;
+};
+
+__host__ __device__ inline Schedule make_schedule(int M, int N, int num_ctas) {
+  Schedule s;
+  s.tiles_m = (M + BM - 1) / BM;
+  s.tiles_n = (N + BN - 1) / BN;
+  const int tiles = s.tiles_m * s.tiles_n;
+  const int rem = tiles % num_ctas;
+  s.split = 1;
+  if (rem != 0 && tiles > rem) {  // only behind at least one complete wave
+    // cost of the tail in tile times: ceil(rem * f / P) / f
+    int best_num = 1, best_den = 1;  // f = 1: one more wave
+    for (int f = 2; f <= 4; f *= 2) {
+      const int waves = (rem * f + num_ctas - 1) / num_ctas;
+      if (waves * best_den < best_num * f) {
+        best_num = waves;
+        best_den = f;
+        s.split = f;
+      }
+    }
+  }
+  s.full_tiles = s.split == 1 ? tiles : tiles - rem;
+  s.total_units = s.full_tiles + (tiles - s.full_tiles) * s.split;
+  return s;
+}
+
+__device__ __forceinline__ WorkUnit work_unit(int unit, const Schedule& s) {
+  int tile = unit, strip = 0, width = BN;
+  if (unit >= s.full_tiles) {
+    const int u = unit - s.full_tiles;
+    tile = s.full_tiles + u / s.split;
+    strip = u % s.split;
+    width = BN / s.split;
+  }
+  const int per_group = GROUP_M * s.tiles_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
-  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int rows = min(GROUP_M, s.tiles_m - first_m);
   const int in_group = tile - group * per_group;
-  return {first_m + in_group % rows, in_group / rows};
+  return {first_m + in_group % rows, (in_group / rows) * BN + strip * width, width};
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
                     void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
                     uint32_t fmt, float alpha, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -75,9 +115,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM;
-  const int tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const Schedule sched = make_schedule(M, N, gridDim.x);
+  const int num_units = sched.total_units;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -109,9 +148,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-        const int m0 = tc.m * BM, n0 = tc.n * BN;
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const WorkUnit wu = work_unit(unit, sched);
+        const int m0 = wu.m * BM, n0 = wu.n0;
+        const uint32_t stage_tx = A_BYTES + wu.width * BK * 2;
+        const CUtensorMap* tb_k = wu.width == BN ? &tmap_b : (wu.width == BN / 2 ? &tmap_b_half : &tmap_b_quarter);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -120,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint32_t bar = full_bar(stage);
-          mbar_arrive_expect_tx(bar, STAGE_BYTES);
+          mbar_arrive_expect_tx(bar, stage_tx);
           const int k0 = kb * BK;
           if (A_MN) {
             // global [K rows][M contiguous]: one 64(M) x 64(K) box per 64 rows of the tile
@@ -130,10 +171,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tma_load_2d(sa, &tmap_a, bar, k0, m0);  // global [M rows][K contiguous]: 64(K) x 128(M)
           }
           if (B_MN) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmap_b, bar, n0 + 64 * j, k0);
+            for (int j = 0; j < wu.width / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmap_b, bar, n0 + 64 * j, k0);
           } else {
-            tma_load_2d(sb, &tmap_b, bar, k0, n0);  // 64(K) x 256(N)
+            tma_load_2d(sb, tb_k, bar, k0, n0);  // 64(K) x width(N)
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -146,7 +186,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(fmt, BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      const uint32_t idesc_full = make_idesc_f16(fmt, BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       // K-major: 64-element (128 B) rows, 8-row groups 1024 B apart; a k-step of 16 = 32 B.
       // MN-major: 64-wide boxes of BK rows; 8-row k-groups 1024 B apart; k-step of 16 rows = 2048 B.
       constexpr uint32_t A_LBO = A_MN ? BK * 128 : 0, B_LBO = B_MN ? BK * 128 : 0;
@@ -156,7 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int width = unit >= sched.full_tiles ? BN / sched.split : BN;
+        const uint32_t idesc = width == BN ? idesc_full : make_idesc_f16(fmt, BM, width, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -194,15 +236,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-      const int row = tc.m * BM + quarter * 32 + lane;
-      const int n0 = tc.n * BN;
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+      const WorkUnit wu = work_unit(unit, sched);
+      const int row = wu.m * BM + quarter * 32 + lane;
+      const int n0 = wu.n0;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < wu.width / 32; ++c) {
         const int col = n0 + c * 32;
         if (col >= N) break;  // warp-uniform
         uint32_t v[32];
@@ -371,7 +413,7 @@ const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t ro
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
-static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* d, const void* bias, int M, int N, int K,
+static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, void* d, const void* bias, int M, int N, int K,
                               long long ldd, uint32_t fmt, float alpha, int* status, int num_sms, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
   static bool configured = false;
@@ -382,14 +424,15 @@ static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, d, bias, M, N, K, ldd, fmt, alpha, status);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, status);
   return cudaGetLastError();
 }
 
 template <bool A_MN, bool B_MN>
-static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, int num_sms, cudaStream_t s) {
+static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
+                                     int num_sms, cudaStream_t s) {
 #define ELFB_LAUNCH(F32, ACC, BI) \
-  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.status, num_sms, s)
+  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.status, num_sms, s)
   if (g.out_f32) {
     if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
     else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }
@@ -402,7 +445,7 @@ static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, c
 
 const char* gemm_tcgen05(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return nullptr;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tb2, tb4;
   const char* err;
   if (g.a_mn_major) err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, BK);
   else              err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, BM);
@@ -410,13 +453,23 @@ const char* gemm_tcgen05(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   if (g.b_mn_major) err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, BK);
   else              err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN);
   if (err) return err;
+  // K-major B strips of the split tail wave need their own box heights; MN-major B is
+  // fetched in 64-wide boxes whatever the strip width
+  tb2 = tb;
+  tb4 = tb;
+  if (!g.b_mn_major) {
+    err = make_tmap_2d(&tb2, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 2);
+    if (err) return err;
+    err = make_tmap_2d(&tb4, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 4);
+    if (err) return err;
+  }
   const int esz = g.out_f32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(g.d) & 15) != 0 || (g.ldd * esz) % 16 != 0) return "GEMM output must be 16-byte aligned with a 16-byte multiple row pitch";
   cudaError_t e;
-  if (g.a_mn_major && g.b_mn_major) e = dispatch_epilogue<true, true>(g, ta, tb, num_sms, stream);
-  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_epilogue<false, true>(g, ta, tb, num_sms, stream);
-  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_epilogue<false, false>(g, ta, tb, num_sms, stream);
-  else e = dispatch_epilogue<true, false>(g, ta, tb, num_sms, stream);
+  if (g.a_mn_major && g.b_mn_major) e = dispatch_epilogue<true, true>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_epilogue<false, true>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_epilogue<false, false>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else e = dispatch_epilogue<true, false>(g, ta, tb, tb2, tb4, num_sms, stream);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

@@ -124,8 +124,7 @@ class LlamaDecoderLayer(nn.Module):
         # rotate in place
         qkv = self.wqkv(self.norm1(x).view(b * s, d))
         qkv = _f.rope_(qkv, cos, sin, hq + hkv, hd, s).view(b, s, hq + 2 * hkv, hd)
-        q, k, v = qkv[:, :, :hq], qkv[:, :, hq : hq + hkv], qkv[:, :, hq + hkv :]
-        a = _attn.attention(q, k, v, causal=True).reshape(b, s, hq * hd)
+        a = _attn.attention_packed(qkv, hq, hkv, causal=True).reshape(b, s, hq * hd)
         h2, x = _f.add_rms_norm(self.wo(a), x, self.norm2.weight, self.norm2.eps)
         return x + self.w_down(_f.swiglu(self.w_gate_up(h2)))
 
