@@ -23,7 +23,7 @@ int sm_count() {
 // d (+)= alpha * op(a) . op(b) (+ bias).  Logical shapes: d [M,N]; a is [M,K] (a_mn_major=false,
 // K contiguous) or [K,M] (a_mn_major=true, M contiguous); b is [N,K] or [K,N] likewise.
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const c10::optional<at::Tensor>& bias, bool a_mn_major,
-          bool b_mn_major, bool accumulate, double alpha, const c10::optional<at::Tensor>& status) {
+          bool b_mn_major, bool accumulate, double alpha, const c10::optional<at::Tensor>& status, int64_t variant, bool split_tail) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda(), "elf_b200 GEMM needs CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "elf_b200 GEMM takes 2-D tensors");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "innermost dimension must be contiguous");
@@ -49,6 +49,8 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const c10::op
   TORCH_CHECK(g.out_f32 || d.scalar_type() == a.scalar_type(), "D must be fp32 or the operand dtype");
   g.accumulate = accumulate;
   g.alpha = (float)alpha;
+  g.variant = (int)variant;
+  g.split_tail = split_tail;
   if (bias.has_value() && bias->defined()) {
     TORCH_CHECK(bias->scalar_type() == d.scalar_type() && bias->numel() == g.N && bias->is_contiguous(), "bias must be a contiguous [N] tensor of D's dtype");
     TORCH_CHECK(g.N % 8 == 0, "bias epilogue needs N % 8 == 0");
@@ -67,7 +69,8 @@ void register_host_runtime(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM: d (+)= alpha * a.b (+ bias)", py::arg("a"), py::arg("b"), py::arg("d"),
         py::arg("bias") = c10::nullopt, py::arg("a_mn_major") = false, py::arg("b_mn_major") = false,
-        py::arg("accumulate") = false, py::arg("alpha") = 1.0, py::arg("status") = c10::nullopt);
+        py::arg("accumulate") = false, py::arg("alpha") = 1.0, py::arg("status") = c10::nullopt, py::arg("variant") = 0,
+        py::arg("split_tail") = true);
   register_fused_ops(m);
   register_host_runtime(m);
 }

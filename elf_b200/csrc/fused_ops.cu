@@ -127,69 +127,90 @@ __global__ void __launch_bounds__(RMS_THREADS) rmsnorm_fwd_kernel(const Bf16x8* 
   }
 }
 
-// Each block walks rows block, block+grid, ... ; per row: dx; per column: partial dw in registers.
-constexpr int RMS_BWD_BLOCKS = 296;  // 2 per SM
+// Backward in two bandwidth-shaped kernels.
+//   dx:  one block per row, the row lives in registers (same shape as the forward).
+//   dw:  grid (dim/256 column slabs, RMS_DW_SPLITS row groups); a block's 256 threads form
+//        32 column groups (8 columns each) x 8 row lanes and walk the rows of their group;
+//        the 8 lanes are summed through shared memory and written as one partial row.
+constexpr int RMS_DW_SPLITS = 64;
 
 template <bool DRES>
-__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
-                                                                  const Bf16x8* __restrict__ w, const float* __restrict__ rstd,
-                                                                  const Bf16x8* __restrict__ dres, Bf16x8* __restrict__ dx,
-                                                                  float* __restrict__ dw_partial, int rows, int dim8,
-                                                                  float inv_dim) {
+__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_dx_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
+                                                                     const Bf16x8* __restrict__ w, const float* __restrict__ rstd,
+                                                                     const Bf16x8* __restrict__ dres, Bf16x8* __restrict__ dx,
+                                                                     int dim8, float inv_dim) {
   __shared__ float red[32];
-  float wv[RMS_MAX_VEC][8], dwacc[RMS_MAX_VEC][8];
-#pragma unroll
-  for (int it = 0; it < RMS_MAX_VEC; ++it) {
-    const int i = threadIdx.x + it * RMS_THREADS;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[it][j] = 0.f;
-    if (i < dim8) unpack8(w[i], wv[it]);
-  }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rs = rstd[row];
-    float xv[RMS_MAX_VEC][8], gv[RMS_MAX_VEC][8];
-    float dot = 0.f;
-#pragma unroll
-    for (int it = 0; it < RMS_MAX_VEC; ++it) {
-      const int i = threadIdx.x + it * RMS_THREADS;
-      if (i < dim8) {
-        unpack8(x[row * dim8 + i], xv[it]);
-        unpack8(dy[row * dim8 + i], gv[it]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          dwacc[it][j] += gv[it][j] * xv[it][j] * rs;
-          gv[it][j] *= wv[it][j];
-          dot += gv[it][j] * xv[it][j];
-        }
-      }
-    }
-    dot = block_sum(dot, red);
-    const float c = dot * inv_dim * rs * rs * rs;
-#pragma unroll
-    for (int it = 0; it < RMS_MAX_VEC; ++it) {
-      const int i = threadIdx.x + it * RMS_THREADS;
-      if (i < dim8) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = gv[it][j] * rs - xv[it][j] * c;
-        if (DRES) {
-          float r[8];
-          unpack8(dres[row * dim8 + i], r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
-        }
-        dx[row * dim8 + i] = pack8(o);
-      }
-    }
-  }
+  const long long row = blockIdx.x;
+  const float rs = rstd[row];
+  float xv[RMS_MAX_VEC][8], gv[RMS_MAX_VEC][8];
+  float dot = 0.f;
 #pragma unroll
   for (int it = 0; it < RMS_MAX_VEC; ++it) {
     const int i = threadIdx.x + it * RMS_THREADS;
     if (i < dim8) {
-      float* dst = dw_partial + (long long)blockIdx.x * dim8 * 8 + (long long)i * 8;
-      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[it][0], dwacc[it][1], dwacc[it][2], dwacc[it][3]);
-      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[it][4], dwacc[it][5], dwacc[it][6], dwacc[it][7]);
+      float wv[8];
+      unpack8(x[row * dim8 + i], xv[it]);
+      unpack8(dy[row * dim8 + i], gv[it]);
+      unpack8(w[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        gv[it][j] *= wv[j];
+        dot += gv[it][j] * xv[it][j];
+      }
     }
+  }
+  dot = block_sum(dot, red);
+  const float c = dot * inv_dim * rs * rs * rs;
+#pragma unroll
+  for (int it = 0; it < RMS_MAX_VEC; ++it) {
+    const int i = threadIdx.x + it * RMS_THREADS;
+    if (i < dim8) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = gv[it][j] * rs - xv[it][j] * c;
+      if (DRES) {
+        float r[8];
+        unpack8(dres[row * dim8 + i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      dx[row * dim8 + i] = pack8(o);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
+                                                             const float* __restrict__ rstd, float* __restrict__ dw_partial, int rows,
+                                                             int dim8) {
+  __shared__ float red[8][32][8];
+  const int cg = threadIdx.x & 31;   // column group within the slab
+  const int lane_r = threadIdx.x >> 5;  // row lane 0..7
+  const int col8 = blockIdx.x * 32 + cg;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col8 < dim8) {
+    for (long long row = (long long)blockIdx.y * 8 + lane_r; row < rows; row += (long long)gridDim.y * 8) {
+      float a[8], b[8];
+      unpack8(dy[row * dim8 + col8], a);
+      unpack8(x[row * dim8 + col8], b);
+      const float rs = rstd[row];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * rs;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[lane_r][cg][j] = acc[j];
+  __syncthreads();
+  if (lane_r == 0 && col8 < dim8) {
+    float s[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) s[j] += red[r][cg][j];
+    }
+    float* dst = dw_partial + ((long long)blockIdx.y * dim8 + col8) * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(s[0], s[1], s[2], s[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(s[4], s[5], s[6], s[7]);
   }
 }
 
@@ -450,22 +471,26 @@ cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, 
   return cudaGetLastError();
 }
 
-int rmsnorm_backward_blocks(int rows) { return rows < RMS_BWD_BLOCKS ? (rows > 0 ? rows : 1) : RMS_BWD_BLOCKS; }
+int rmsnorm_backward_blocks(int rows) { return RMS_DW_SPLITS; }
 
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
                              float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
   if (dim % 8 || dim > RMS_THREADS * RMS_MAX_VEC * 8) return cudaErrorInvalidValue;
-  const int dim8 = dim / 8, nb = rmsnorm_backward_blocks(rows);
+  const int dim8 = dim / 8;
   if (dres_in)
-    rmsnorm_bwd_kernel<true><<<nb, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd,
-                                                        (const Bf16x8*)dres_in, (Bf16x8*)dx, dw_partial, rows, dim8, 1.f / dim);
+    rmsnorm_bwd_dx_kernel<true><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd,
+                                                             (const Bf16x8*)dres_in, (Bf16x8*)dx, dim8, 1.f / dim);
   else
-    rmsnorm_bwd_kernel<false><<<nb, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr,
-                                                         (Bf16x8*)dx, dw_partial, rows, dim8, 1.f / dim);
+    rmsnorm_bwd_dx_kernel<false><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr,
+                                                              (Bf16x8*)dx, dim8, 1.f / dim);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, dw, nb, dim, accumulate_dw);
+  const dim3 grid((dim8 + 31) / 32, RMS_DW_SPLITS);
+  rmsnorm_bwd_dw_kernel<<<grid, 256, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, rstd, dw_partial, rows, dim8);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, dw, RMS_DW_SPLITS, dim, accumulate_dw);
   return cudaGetLastError();
 }
 

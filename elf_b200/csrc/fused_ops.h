@@ -10,7 +10,7 @@ namespace elfb {
 // y = (x [+ residual]) * rsqrt(mean(.^2) + eps) * w ; optionally writes h = x + residual.
 cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, void* y, void* h, float* rstd, int rows,
                             int dim, float eps, cudaStream_t s);
-// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) [+ dres_in]; dw_partial[block][dim] = sum over the block's rows of dy*x*rstd.
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) [+ dres_in]; dw_partial[group][dim] = sum over a group of rows of dy*x*rstd.
 // `dw_partial` is scratch of rmsnorm_backward_blocks(rows) * dim floats; `dw` (fp32 [dim]) receives (+=) the column sums.
 int rmsnorm_backward_blocks(int rows);
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,

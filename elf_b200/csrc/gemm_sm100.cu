@@ -25,6 +25,7 @@
 #include <cstdio>
 
 #include "sm100_ptx.cuh"
+#include "gemm_epilogue.cuh"
 #include "gemm_sm100.h"
 
 namespace elfb {
@@ -54,7 +55,7 @@ struct Schedule {
   int tiles_m, tiles_n, full_tiles, split, total_units;
 };
 
-__host__ __device__ inline Schedule make_schedule(int M, int N, int num_ctas) {
+__host__ __device__ inline Schedule make_schedule(int M, int N, int num_ctas, int max_split) {
   Schedule s;
   s.tiles_m = (M + BM - 1) / BM;
   s.tiles_n = (N + BN - 1) / BN;
@@ -64,7 +65,7 @@ __host__ __device__ inline Schedule make_schedule(int M, int N, int num_ctas) {
   if (rem != 0 && tiles > rem) {  // only behind at least one complete wave
     // cost of the tail in tile times: ceil(rem * f / P) / f
     int best_num = 1, best_den = 1;  // f = 1: one more wave
-    for (int f = 2; f <= 4; f *= 2) {
+    for (int f = 2; f <= max_split; f *= 2) {
       const int waves = (rem * f + num_ctas - 1) / num_ctas;
       if (waves * best_den < best_num * f) {
         best_num = waves;
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
                     void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
-                    uint32_t fmt, float alpha, int* __restrict__ status) {
+                    uint32_t fmt, float alpha, int max_split, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -115,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const Schedule sched = make_schedule(M, N, gridDim.x);
+  const Schedule sched = make_schedule(M, N, gridDim.x, max_split);
   const int num_units = sched.total_units;
   const int k_blocks = (K + BK - 1) / BK;
 
@@ -250,86 +251,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + c * 32, v);
         tmem_ld_wait();
-        if (row < M) {
-          const bool full_chunk = col + 32 <= N;
-          if (OUT_F32) {
-            float* dst = reinterpret_cast<float*>(d_ptr) + (long long)row * ldd + col;
-            if (full_chunk) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o;
-                o.x = __uint_as_float(v[j]) * alpha;
-                o.y = __uint_as_float(v[j + 1]) * alpha;
-                o.z = __uint_as_float(v[j + 2]) * alpha;
-                o.w = __uint_as_float(v[j + 3]) * alpha;
-                if (BIAS) {
-                  const float* b = reinterpret_cast<const float*>(bias_ptr) + col + j;
-                  o.x += b[0]; o.y += b[1]; o.z += b[2]; o.w += b[3];
-                }
-                if (ACCUM) {
-                  const float4 p = *reinterpret_cast<const float4*>(dst + j);
-                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float o = __uint_as_float(v[j]) * alpha;
-                if (BIAS) o += reinterpret_cast<const float*>(bias_ptr)[col + j];
-                if (ACCUM) o += dst[j];
-                dst[j] = o;
-              }
-            }
-          } else {
-            // 16-bit output (same format as the operands)
-            uint16_t* dst = reinterpret_cast<uint16_t*>(d_ptr) + (long long)row * ldd + col;
-            const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(bias_ptr);
-            auto to_f = [&](uint16_t h) -> float {
-              return fmt == 1u ? __bfloat162float(__ushort_as_bfloat16(h)) : __half2float(__ushort_as_half(h));
-            };
-            auto pack2 = [&](float a, float b) -> uint32_t { return fmt == 1u ? pack_bf16x2(a, b) : pack_f16x2(a, b); };
-            if (full_chunk) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float f[8];
-#pragma unroll
-                for (int t = 0; t < 8; ++t) f[t] = __uint_as_float(v[j + t]) * alpha;
-                if (BIAS) {
-                  const uint4 bq = *reinterpret_cast<const uint4*>(bias16 + col + j);
-                  const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
-#pragma unroll
-                  for (int t = 0; t < 4; ++t) {
-                    f[2 * t] += to_f(uint16_t(bw[t] & 0xffff));
-                    f[2 * t + 1] += to_f(uint16_t(bw[t] >> 16));
-                  }
-                }
-                if (ACCUM) {
-                  const uint4 pq = *reinterpret_cast<const uint4*>(dst + j);
-                  const uint32_t pw[4] = {pq.x, pq.y, pq.z, pq.w};
-#pragma unroll
-                  for (int t = 0; t < 4; ++t) {
-                    f[2 * t] += to_f(uint16_t(pw[t] & 0xffff));
-                    f[2 * t + 1] += to_f(uint16_t(pw[t] >> 16));
-                  }
-                }
-                uint4 o;
-                o.x = pack2(f[0], f[1]);
-                o.y = pack2(f[2], f[3]);
-                o.z = pack2(f[4], f[5]);
-                o.w = pack2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float o = __uint_as_float(v[j]) * alpha;
-                if (BIAS) o += to_f(bias16[col + j]);
-                if (ACCUM) o += to_f(dst[j]);
-                const uint32_t p = pack2(o, 0.f);
-                dst[j] = uint16_t(p & 0xffff);
-              }
-            }
-          }
-        }
+        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -414,7 +336,7 @@ const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t ro
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, void* d, const void* bias, int M, int N, int K,
-                              long long ldd, uint32_t fmt, float alpha, int* status, int num_sms, cudaStream_t stream) {
+                              long long ldd, uint32_t fmt, float alpha, int max_split, int* status, int num_sms, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
   static bool configured = false;
   if (!configured) {
@@ -424,7 +346,7 @@ static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, cons
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, status);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, max_split, status);
   return cudaGetLastError();
 }
 
@@ -432,7 +354,7 @@ template <bool A_MN, bool B_MN>
 static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
                                      int num_sms, cudaStream_t s) {
 #define ELFB_LAUNCH(F32, ACC, BI) \
-  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.status, num_sms, s)
+  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.split_tail ? 4 : 1, g.status, num_sms, s)
   if (g.out_f32) {
     if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
     else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }
@@ -445,6 +367,7 @@ static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, c
 
 const char* gemm_tcgen05(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return nullptr;
+  if (g.variant == 1 && num_sms >= 2) return gemm_tcgen05_pair(g, num_sms, stream);
   CUtensorMap ta, tb, tb2, tb4;
   const char* err;
   if (g.a_mn_major) err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, BK);

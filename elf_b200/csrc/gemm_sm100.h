@@ -17,9 +17,14 @@ struct GemmArgs {
   bool accumulate = false;     // D += alpha * A.B instead of D = alpha * A.B
   float alpha = 1.0f;
   int* status = nullptr;       // optional device int[4] error record
+  int variant = 0;             // 0 = single-CTA kernel, 1 = CTA-pair kernel (cta_group::2)
+  bool split_tail = true;      // cut the tiles of the last, partial wave into column strips
 };
 
 // Returns nullptr on success, otherwise a static description of the failure.
 const char* gemm_tcgen05(const GemmArgs& args, int num_sms, cudaStream_t stream);
+
+// Same contract, CTA-pair kernel (gemm_sm100_2cta.cu).
+const char* gemm_tcgen05_pair(const GemmArgs& args, int num_sms, cudaStream_t stream);
 
 }  // namespace elfb

@@ -1,0 +1,357 @@
+// CTA-pair variant of the tcgen05 GEMM: two CTAs on neighbouring SMs (a cluster of 2) share
+// one 256x256 output tile through `tcgen05.mma.cta_group::2`.
+//
+// Each CTA owns 128 of the tile's 256 rows: it TMA-loads its own A slab (128 x 64) and HALF
+// of the B slab (128 of the 256 B rows) into its own shared memory and receives its 128
+// accumulator rows in its own TMEM.  Per flop, each SM therefore reads half as much B from
+// shared memory as in the single-CTA kernel (and fetches half as much from L2), which is
+// what lets the tensor pipe run closer to its peak under the power cap.
+//
+// Synchronisation (every wait bounded, see sm100_ptx.cuh):
+//   full[s]      lives in the EVEN CTA (the leader).  The leader's producer arms it with the
+//                byte count of both CTAs' loads; both CTAs' TMA copies complete on it
+//                (the odd CTA addresses it through the cluster window; no multicast).
+//   empty[s]     one per CTA; the leader's MMA thread commits to both after the MMAs that
+//                read stage s.
+//   acc_full[a]  one per CTA; committed by the leader after the last MMA of a tile.
+//   acc_empty[a] in the leader; the epilogue warps of both CTAs arrive on it (8 arrivals).
+// Only the leader's MMA thread issues MMAs.  TMEM is allocated and freed with the
+// cta_group::2 forms by warp 1 of both CTAs.
+
+#include <cstdio>
+
+#include "sm100_ptx.cuh"
+#include "gemm_epilogue.cuh"
+#include "gemm_sm100.h"
+
+namespace elfb {
+
+namespace pair {
+
+constexpr int BM = 128;          // rows per CTA (256 per pair)
+constexpr int BN = 256;          // columns per pair tile
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
+constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of the B slab
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 4;  // in units of 256-row pair tiles
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+
+struct WorkUnit {
+  int m, n0, width;
+};
+struct Schedule {
+  int tiles_m, tiles_n, full_tiles, split, total_units;
+};
+
+__host__ __device__ inline Schedule make_schedule(int M, int N, int num_pairs, int max_split) {
+  Schedule s;
+  s.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  s.tiles_n = (N + BN - 1) / BN;
+  const int tiles = s.tiles_m * s.tiles_n;
+  const int rem = tiles % num_pairs;
+  s.split = 1;
+  if (rem != 0 && tiles > rem) {
+    int best_num = 1, best_den = 1;
+    for (int f = 2; f <= max_split; f *= 2) {
+      const int waves = (rem * f + num_pairs - 1) / num_pairs;
+      if (waves * best_den < best_num * f) {
+        best_num = waves;
+        best_den = f;
+        s.split = f;
+      }
+    }
+  }
+  s.full_tiles = s.split == 1 ? tiles : tiles - rem;
+  s.total_units = s.full_tiles + (tiles - s.full_tiles) * s.split;
+  return s;
+}
+
+__device__ __forceinline__ WorkUnit work_unit(int unit, const Schedule& s) {
+  int tile = unit, strip = 0, width = BN;
+  if (unit >= s.full_tiles) {
+    const int u = unit - s.full_tiles;
+    tile = s.full_tiles + u / s.split;
+    strip = u % s.split;
+    width = BN / s.split;
+  }
+  const int per_group = GROUP_M * s.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, s.tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  return {first_m + in_group % rows, (in_group / rows) * BN + strip * width, width};
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
+                         void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
+                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + size_t(STAGES) * STAGE_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader, 1 = peer
+  const bool leader = cta == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const Schedule sched = make_schedule(M, N, num_pairs, max_split);
+  const int num_units = sched.total_units;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // used in the leader only: its producer's arrive.expect_tx
+      mbar_init(empty_bar(s), 1);  // one commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);  // used in the leader only: 4 epilogue warps of each CTA
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone touches the peer's
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = pair_id; unit < num_units && ok; unit += num_pairs) {
+        const WorkUnit wu = work_unit(unit, sched);
+        const int m0 = wu.m * (2 * BM) + int(cta) * BM;  // this CTA's 128 rows
+        const int half = wu.width / 2;
+        const int n0 = wu.n0 + int(cta) * half;          // this CTA's half of the B rows
+        const uint32_t pair_tx = 2u * (A_BYTES + half * BK * 2);
+        const CUtensorMap* tb_k = wu.width == BN ? &tmap_b : (wu.width == BN / 2 ? &tmap_b_half : &tmap_b_quarter);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t bar = map_to_cta(full_bar(stage), 0);  // the leader's barrier
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), pair_tx);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmap_a, bar, m0 + 64 * j, k0);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
+          }
+          if (B_MN) {
+            for (int j = 0; j < half / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, bar, n0 + 64 * j, k0);
+          } else {
+            tma_load_2d_pair(sb, tb_k, bar, k0, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 0, B_LBO = B_MN ? BK * 128 : 0;
+      constexpr uint32_t A_KSTEP = A_MN ? UMMA_K * 128 : UMMA_K * 2, B_KSTEP = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int unit = pair_id; unit < num_units && ok; unit += num_pairs) {
+        const int width = unit >= sched.full_tiles ? BN / sched.split : BN;
+        const uint32_t idesc = make_idesc_f16(fmt, 2 * BM, width, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024);
+            umma_ss_pair(tmem_d, da, db, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit_pair(map_to_cta(empty_bar(stage), 0));
+          umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(map_to_cta(acc_full_bar(acc), 0));
+        umma_commit_pair(map_to_cta(acc_full_bar(acc), 1));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t leader_acc_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
+    for (int unit = pair_id; unit < num_units; unit += num_pairs) {
+      const WorkUnit wu = work_unit(unit, sched);
+      const int row = wu.m * (2 * BM) + int(cta) * BM + quarter * 32 + lane;
+      const int n0 = wu.n0;
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < wu.width / 32; ++c) {
+        const int col = n0 + c * 32;
+        if (col >= N) break;
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {
+      }
+      if (status != nullptr && atomicCAS(status, kOk, kErrBarrierTimeout) == kOk) {
+        status[1] = 1000000 + blockIdx.x;
+        status[2] = M;
+        status[3] = N;
+      }
+    }
+    __syncthreads();
+  }
+  cluster_sync_all();  // the peer may still be signalling barriers in this CTA's shared memory
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace pair
+
+const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                         uint32_t box_rows);
+
+template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
+static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, const GemmArgs& g,
+                               int num_sms, cudaStream_t stream) {
+  using namespace pair;
+  auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  const int max_split = g.b_mn_major ? 2 : 4;  // MN-major B is fetched in 64-wide boxes per CTA
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha,
+                                                       max_split, g.status);
+  return cudaGetLastError();
+}
+
+template <bool A_MN, bool B_MN>
+static cudaError_t dispatch_pair(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
+                                 int num_sms, cudaStream_t s) {
+#define ELFB_LAUNCH(F32, ACC, BI) return launch_pair<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g, num_sms, s)
+  if (g.out_f32) {
+    if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
+    else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }
+  } else {
+    if (g.accumulate) { if (g.bias) ELFB_LAUNCH(false, true, true); else ELFB_LAUNCH(false, true, false); }
+    else              { if (g.bias) ELFB_LAUNCH(false, false, true); else ELFB_LAUNCH(false, false, false); }
+  }
+#undef ELFB_LAUNCH
+}
+
+const char* gemm_tcgen05_pair(const GemmArgs& g, int num_sms, cudaStream_t stream) {
+  using namespace pair;
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return nullptr;
+  CUtensorMap ta, tb, tb2, tb4;
+  const char* err;
+  if (g.a_mn_major) err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, BK);
+  else              err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, BM);
+  if (err) return err;
+  if (g.b_mn_major) {
+    err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, BK);
+    if (err) return err;
+    tb2 = tb;
+    tb4 = tb;
+  } else {
+    // per-CTA B boxes hold half of the unit's rows: 128, 64 or 32
+    err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 2);
+    if (err) return err;
+    err = make_tmap_2d(&tb2, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 4);
+    if (err) return err;
+    err = make_tmap_2d(&tb4, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 8);
+    if (err) return err;
+  }
+  const int esz = g.out_f32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(g.d) & 15) != 0 || (g.ldd * esz) % 16 != 0) return "GEMM output must be 16-byte aligned with a 16-byte multiple row pitch";
+  cudaError_t e;
+  if (g.a_mn_major && g.b_mn_major) e = dispatch_pair<true, true>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_pair<false, true>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_pair<false, false>(g, ta, tb, tb2, tb4, num_sms, stream);
+  else e = dispatch_pair<true, false>(g, ta, tb, tb2, tb4, num_sms, stream);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace elfb

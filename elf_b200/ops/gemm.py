@@ -33,9 +33,13 @@ __all__ = [
     "status",
     "check_status",
     "set_enabled",
+    "set_variant",
 ]
 
 _ENABLED = os.environ.get("ELF_B200_DISABLE_KERNELS", "0") != "1"
+# 0 = one CTA per 128x256 tile, 1 = CTA pairs (cta_group::2) on 256x256 tiles
+_VARIANT = int(os.environ.get("ELF_B200_GEMM_VARIANT", "1"))
+_SPLIT_TAIL = os.environ.get("ELF_B200_GEMM_SPLIT_TAIL", "1") != "0"
 _STATUS: Dict[int, torch.Tensor] = {}
 _DTYPES = (torch.bfloat16, torch.float16)
 
@@ -44,6 +48,12 @@ def set_enabled(flag: bool) -> None:
     """Switch the kernels off (torch ops are used instead) — for A/B numerics tests."""
     global _ENABLED
     _ENABLED = bool(flag)
+
+
+def set_variant(variant: int, split_tail: bool = True) -> None:
+    """Select the kernel variant (0 single CTA, 1 CTA pair) and the tail-wave splitting."""
+    global _VARIANT, _SPLIT_TAIL
+    _VARIANT, _SPLIT_TAIL = int(variant), bool(split_tail)
 
 
 def status(device=None) -> torch.Tensor:
@@ -92,14 +102,14 @@ def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     # Function, or later in-place ops on it (RoPE) would be rejected
     y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
     b = None if bias is None else bias.to(x.dtype).contiguous()
-    _ext.get().gemm(x2, _rows(w), y.view(-1, w.shape[0]), b, False, False, False, 1.0, status(x.device))
+    _ext.get().gemm(x2, _rows(w), y.view(-1, w.shape[0]), b, False, False, False, 1.0, status(x.device), _VARIANT, _SPLIT_TAIL)
     return y
 
 
 def linear_input_grad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     dy2 = _rows(dy)
     dx = torch.empty((*dy.shape[:-1], w.shape[1]), dtype=dy.dtype, device=dy.device)
-    _ext.get().gemm(dy2, _rows(w), dx.view(-1, w.shape[1]), None, False, True, False, 1.0, status(dy.device))
+    _ext.get().gemm(dy2, _rows(w), dx.view(-1, w.shape[1]), None, False, True, False, 1.0, status(dy.device), _VARIANT, _SPLIT_TAIL)
     return dx
 
 
@@ -110,7 +120,7 @@ def linear_weight_grad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Te
     accumulate = out is not None
     if out is None:
         out = torch.empty((dy2.shape[1], x2.shape[1]), dtype=out_dtype or dy.dtype, device=dy.device)
-    _ext.get().gemm(dy2, x2, out, None, True, True, accumulate, float(alpha), status(dy.device))
+    _ext.get().gemm(dy2, x2, out, None, True, True, accumulate, float(alpha), status(dy.device), _VARIANT, _SPLIT_TAIL)
     return out
 
 
@@ -118,5 +128,5 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, out_dtype=None) -> torch.Tensor:
     """``a[M,K] · b[N,K]ᵀ`` for plain 2-D use."""
     a2, b2 = _rows(a), _rows(b)
     d = torch.empty((a2.shape[0], b2.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
-    _ext.get().gemm(a2, b2, d, None, False, False, False, 1.0, status(a.device))
+    _ext.get().gemm(a2, b2, d, None, False, False, False, 1.0, status(a.device), _VARIANT, _SPLIT_TAIL)
     return d

@@ -152,6 +152,17 @@ def pin_get_attrs(parts: List[List[fx.Node]]) -> List[List[fx.Node]]:
     return out
 
 
+def pin_placeholders(parts: List[List[fx.Node]]) -> List[List[fx.Node]]:
+    """All model inputs enter through the first part (the only stage the runtime feeds);
+    later parts that use one receive it as a pass-through output of that part."""
+    strays = [nd for part in parts[1:] for nd in part if nd.op == "placeholder"]
+    if not strays:
+        return parts
+    out = [[nd for nd in part if nd not in strays] for part in parts]
+    out[0] = strays + out[0]
+    return out
+
+
 def _part_io(parts: List[List[fx.Node]]):
     n = len(parts)
     home = {nd: i for i, part in enumerate(parts) for nd in part}
@@ -182,17 +193,19 @@ def _part_io(parts: List[List[fx.Node]]):
                     add_final_outputs(i, arg)
                 continue
             for dep in nd.all_input_nodes:
-                if home.get(dep) == i and dep.op != "placeholder":
+                src = home.get(dep)
+                if src == i:
+                    if dep.op == "placeholder" and dep.target not in inputs[i]:
+                        inputs[i].append(dep.target)
                     continue
+                # a value made (or, for a model input, received) by another part
                 name = dep.target if dep.op == "placeholder" else dep.name
                 if name not in inputs[i]:
                     inputs[i].append(name)
-                if dep.op != "placeholder" and dep in home:
-                    src = home[dep]
-                    if dep.name not in outputs[src]:
-                        outputs[src].append(dep.name)
-                    if src != i:
-                        deps[i].add(src)
+                if src is not None:
+                    if name not in outputs[src]:
+                        outputs[src].append(name)
+                    deps[i].add(src)
     return inputs, outputs, deps
 
 
@@ -219,7 +232,7 @@ def get_inputs_outputs(parts: List[List[fx.Node]]):
     """Inputs/outputs per part (sorted names), parts in dependency order, without their
     placeholder/output nodes.  A final output produced by an earlier part than the one
     holding the graph's ``output`` node is exported by its producer."""
-    parts = pin_get_attrs(parts)
+    parts = pin_placeholders(pin_get_attrs(parts))
     inputs, outputs, deps = _part_io(parts)
     order = _topo_order(deps)
     parts = [parts[i] for i in order]

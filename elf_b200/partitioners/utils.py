@@ -77,31 +77,34 @@ def remove_inplace_leaves(module: fx.GraphModule) -> fx.GraphModule:
     mutating those in place, which would break every stage whose first op is e.g.
     ``relu_`` or ``nn.ReLU(inplace=True)`` (reference ``elf/partitioners/utils.py:149-302``)."""
     g = module.graph
-    tainted = set()
-    for node in g.nodes:  # nodes are in topological order: one pass reaches a fixed point
-        if node.op in ("placeholder", "output"):
-            continue
-        deps = list(node.all_input_nodes)
-        if all(d.op == "placeholder" for d in deps):
-            tainted.add(node)
-        elif node.op == "call_function" and _returns_alias(node.target) and any(d in tainted for d in deps):
-            tainted.add(node)
-        elif node.op == "call_method" and node.target in ("view", "reshape", "transpose", "permute", "squeeze", "unsqueeze", "flatten", "t") and any(
-            d in tainted for d in deps
-        ):
-            tainted.add(node)
     owner = g.owning_module
-    for node in tainted:
-        if node.op == "call_function" and _is_inplace(node.target):
-            node.target = _out_of_place(node.target)
-        elif node.op == "call_method" and node.target.endswith("_") and not node.target.endswith("__") and hasattr(torch.Tensor, node.target[:-1]):
-            node.target = node.target[:-1]
+    view_methods = {"view", "reshape", "transpose", "permute", "squeeze", "unsqueeze", "flatten", "t", "contiguous", "narrow", "select", "expand", "view_as", "__getitem__"}
+    # tensors that share storage with a stage input: the inputs and (chains of) views of them
+    aliases = {nd for nd in g.nodes if nd.op == "placeholder"}
+    for node in g.nodes:  # topological order: one pass reaches the fixed point
+        if node.op in ("placeholder", "output") or not node.all_input_nodes:
+            continue
+        first = node.args[0] if node.args and isinstance(node.args[0], fx.Node) else None
+        touches_input = first in aliases if first is not None else False
+        if not touches_input:
+            continue
+        if node.op == "call_function":
+            if _is_inplace(node.target):
+                node.target = _out_of_place(node.target)  # result is a fresh tensor
+            elif node.kwargs.get("inplace", False):
+                node.kwargs = {**node.kwargs, "inplace": False}
+            elif _returns_alias(node.target) or getattr(node.target, "__name__", "") == "getitem":
+                aliases.add(node)
+        elif node.op == "call_method":
+            name = node.target
+            if name.endswith("_") and not name.endswith("__") and hasattr(torch.Tensor, name[:-1]):
+                node.target = name[:-1]
+            elif name in view_methods:
+                aliases.add(node)
         elif node.op == "call_module" and owner is not None:
             sub = owner.get_submodule(node.target)
             if getattr(sub, "inplace", False):
                 sub.inplace = False
-        if node.op == "call_function" and node.kwargs.get("inplace", False):
-            node.kwargs = {**node.kwargs, "inplace": False}
     module.recompile()
     return module
 
