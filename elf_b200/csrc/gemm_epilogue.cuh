@@ -3,14 +3,18 @@
 #pragma once
 
 #include "sm100_ptx.cuh"
+#include "dp_reduce.h"
 
 namespace elfb {
 
 // D[row, col..col+32) (+)= alpha * v (+ bias); 16-byte vector accesses when the chunk is
-// fully inside the matrix, element-wise on the ragged right edge.
+// fully inside the matrix, element-wise on the ragged right edge.  With a push target
+// (16-bit output only) the finished values are also stored at the same [row, col] of the
+// matrix copy inside every peer GPU's inbox: plain stores to peer memory over NVLink.
 template <bool OUT_F32, bool ACCUM, bool BIAS>
 __device__ __forceinline__ void store_accumulator_chunk(const uint32_t (&v)[32], int row, int col, int M, int N, void* __restrict__ d_ptr,
-                                                        long long ldd, const void* __restrict__ bias_ptr, uint32_t fmt, float alpha) {
+                                                        long long ldd, const void* __restrict__ bias_ptr, uint32_t fmt, float alpha,
+                                                        const PushTarget& push) {
   if (row < M) {
     const bool full_chunk = col + 32 <= N;
     if (OUT_F32) {
@@ -79,14 +83,17 @@ __device__ __forceinline__ void store_accumulator_chunk(const uint32_t (&v)[32],
           o.z = pack2(f[4], f[5]);
           o.w = pack2(f[6], f[7]);
           *reinterpret_cast<uint4*>(dst + j) = o;
+          for (int p = 0; p < push.n_peers; ++p)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(push.peer_out[p]) + (long long)row * ldd + col + j) = o;
         }
       } else {
         for (int j = 0; j < 32 && col + j < N; ++j) {
           float o = __uint_as_float(v[j]) * alpha;
           if (BIAS) o += to_f(bias16[col + j]);
           if (ACCUM) o += to_f(dst[j]);
-          const uint32_t p = pack2(o, 0.f);
-          dst[j] = uint16_t(p & 0xffff);
+          const uint16_t h = uint16_t(pack2(o, 0.f) & 0xffff);
+          dst[j] = h;
+          for (int p = 0; p < push.n_peers; ++p) (reinterpret_cast<uint16_t*>(push.peer_out[p]) + (long long)row * ldd + col)[j] = h;
         }
       }
     }

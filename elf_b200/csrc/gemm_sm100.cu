@@ -26,6 +26,7 @@
 
 #include "sm100_ptx.cuh"
 #include "gemm_epilogue.cuh"
+#include "dp_signal.cuh"
 #include "gemm_sm100.h"
 
 namespace elfb {
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
                     void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
-                    uint32_t fmt, float alpha, int max_split, int* __restrict__ status) {
+                    uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -251,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + c * 32, v);
         tmem_ld_wait();
-        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha);
+        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha, push);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -264,6 +265,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
 
   // ------------------------------------------------------------------ common exit
+  if (push.n_peers > 0) signal_peers_when_last(push.done_counter, push.peer_flag, push.n_peers, push.flag_value);
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
@@ -336,7 +338,7 @@ const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t ro
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, void* d, const void* bias, int M, int N, int K,
-                              long long ldd, uint32_t fmt, float alpha, int max_split, int* status, int num_sms, cudaStream_t stream) {
+                              long long ldd, uint32_t fmt, float alpha, int max_split, int* status, const PushTarget& push, int num_sms, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
   static bool configured = false;
   if (!configured) {
@@ -346,7 +348,7 @@ static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, cons
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, max_split, status);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, max_split, status, push);
   return cudaGetLastError();
 }
 
@@ -354,7 +356,7 @@ template <bool A_MN, bool B_MN>
 static cudaError_t dispatch_epilogue(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
                                      int num_sms, cudaStream_t s) {
 #define ELFB_LAUNCH(F32, ACC, BI) \
-  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.split_tail ? 4 : 1, g.status, num_sms, s)
+  return launch_one<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, g.split_tail ? 4 : 1, g.status, g.push, num_sms, s)
   if (g.out_f32) {
     if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
     else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }

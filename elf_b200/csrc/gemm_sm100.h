@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include "dp_reduce.h"
+
 namespace elfb {
 
 struct GemmArgs {
@@ -19,6 +21,7 @@ struct GemmArgs {
   int* status = nullptr;       // optional device int[4] error record
   int variant = 0;             // 0 = single-CTA kernel, 1 = CTA-pair kernel (cta_group::2)
   bool split_tail = true;      // cut the tiles of the last, partial wave into column strips
+  PushTarget push;             // optional: also store D into peer GPUs' inboxes and flag them (16-bit D only)
 };
 
 // Returns nullptr on success, otherwise a static description of the failure.

@@ -22,6 +22,7 @@
 
 #include "sm100_ptx.cuh"
 #include "gemm_epilogue.cuh"
+#include "dp_signal.cuh"
 #include "gemm_sm100.h"
 
 namespace elfb {
@@ -92,7 +93,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
                          void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
-                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status) {
+                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -248,7 +249,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + c * 32, v);
         tmem_ld_wait();
-        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha);
+        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha, push);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -261,6 +262,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   }
 
   // ------------------------------------------------------------------ common exit
+  if (push.n_peers > 0) signal_peers_when_last(push.done_counter, push.peer_flag, push.n_peers, push.flag_value);
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
@@ -302,9 +304,9 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
-  const int max_split = g.b_mn_major ? 2 : 4;  // MN-major B is fetched in 64-wide boxes per CTA
+  const int max_split = !g.split_tail ? 1 : (g.b_mn_major ? 2 : 4);  // MN-major B is fetched in 64-wide boxes per CTA
   kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha,
-                                                       max_split, g.status);
+                                                       max_split, g.status, g.push);
   return cudaGetLastError();
 }
 

@@ -226,10 +226,12 @@ class PipelineBlock:
                 var_dsts[0].set(var_dsts[0].to_process, mb_id, g)
 
     def backward_params(self, mb_id: int, **options):
+        final = mb_id == getattr(self, "final_w_mb", None)
         with self._timed(f"backward_params({self.id}:{mb_id})"):
             for layer in self.dw_layers():
                 slots = layer.ctx["grad_output"]
                 if len(slots) > mb_id and slots[mb_id] is not None:
+                    layer._final_pass = final  # last W of the step for this stage: gradients are complete
                     layer.backward(mb_id)
 
     def recompute_forward(self, mb_id: int, **options):

@@ -113,14 +113,20 @@ def linear_input_grad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return dx
 
 
-def linear_weight_grad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, alpha: float = 1.0, out_dtype=None) -> torch.Tensor:
+def linear_weight_grad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, alpha: float = 1.0, out_dtype=None, push: Optional[dict] = None) -> torch.Tensor:
     """``out (+)= alpha · dyᵀ·x``; accumulates when ``out`` is given, else allocates
-    (``out_dtype`` defaults to the operand dtype)."""
+    (``out_dtype`` defaults to the operand dtype).  ``push`` (peer addresses, flag addresses,
+    flag value, counter; see ``elf_b200.parallel.dp_sync``) makes the epilogue also store the
+    result into peer GPUs' memory and flag it there."""
     dy2, x2 = _rows(dy), _rows(x)
     accumulate = out is not None
     if out is None:
         out = torch.empty((dy2.shape[1], x2.shape[1]), dtype=out_dtype or dy.dtype, device=dy.device)
-    _ext.get().gemm(dy2, x2, out, None, True, True, accumulate, float(alpha), status(dy.device), _VARIANT, _SPLIT_TAIL)
+    if push:
+        _ext.get().gemm(dy2, x2, out, None, True, True, accumulate, float(alpha), status(dy.device), _VARIANT, _SPLIT_TAIL,
+                        push["push_out"], push["push_flags"], push["push_flag_value"], push["push_counter"])
+    else:
+        _ext.get().gemm(dy2, x2, out, None, True, True, accumulate, float(alpha), status(dy.device), _VARIANT, _SPLIT_TAIL)
     return out
 
 

@@ -40,6 +40,8 @@ class FlatGroup:
             p.data = view
         self.flat_grad = torch.zeros(total, dtype=self.grad_dtype, device=self.device)
         self.attach_grads()
+        for p in params:
+            p._elf_flat_group = self  # lets a later flatten (the optimizer's) adopt this group
 
     def grad_view(self, i: int) -> torch.Tensor:
         p, off = self.params[i], self.offsets[i]
@@ -77,11 +79,22 @@ class FlatGroup:
 
 
 def flatten_parameters(params: Iterable[torch.nn.Parameter], grad_dtype=None) -> List[FlatGroup]:
+    """Groups already built for (all of) these parameters - e.g. by the data-parallel gradient
+    exchange - are reused, so one flat buffer serves both the exchange and the optimizer."""
     buckets: Dict[Tuple[torch.dtype, torch.device], List[torch.nn.Parameter]] = {}
+    adopted: Dict[int, FlatGroup] = {}
     seen = set()
     for p in params:
         if not p.requires_grad or id(p) in seen or p.is_meta:
             continue
         seen.add(id(p))
+        existing = getattr(p, "_elf_flat_group", None)
+        if existing is not None:
+            adopted[id(existing)] = existing
+            continue
         buckets.setdefault((p.dtype, p.device), []).append(p)
-    return [FlatGroup(ps, grad_dtype) for ps in buckets.values()]
+    for g in adopted.values():
+        missing = [q for q in g.params if id(q) not in seen]
+        if missing:
+            raise ValueError("a flat parameter group can only be adopted whole; pass all of its parameters")
+    return list(adopted.values()) + [FlatGroup(ps, grad_dtype) for ps in buckets.values()]

@@ -296,6 +296,8 @@ class Pipeline:
         for block in self.blocks:
             for layer in block.dw_layers():
                 layer.clear()
+        if self.grad_sync is not None:
+            self.grad_sync.begin_step()
 
         if batch is not None:
             batch = [t.to(self.device, non_blocking=True) if t.device != self.device else t for t in batch]
@@ -358,6 +360,9 @@ class Pipeline:
         self.full_schedule = schedule
         mine = {b.id for b in self.blocks}
         self.schedule = [op for op in schedule if op.block_id in mine and op.rank == self.pp_rank]
+        for block in self.blocks:  # the micro-batch whose W pass completes the stage's gradients
+            ws = [op.mb_id for op in self.schedule if op.block_id == block.id and op.op.name == "BACKWARD_PARAMS"]
+            block.final_w_mb = ws[-1] if ws else None
 
     # ------------------------------------------------------------------ parameters
     def parameters(self) -> Iterator[nn.Parameter]:

@@ -191,8 +191,14 @@ class LinearDW(LayerDW, nn.Linear):
         g2, x2 = _flat2d(g), _flat2d(x)
         with torch.no_grad():
             if not g2.is_complex() and _gemm.usable(g2, self.weight) and _gemm.grad_buffer_ok(self.weight):
-                # dW (+)= dYᵀ·X with the accumulation fused in the kernel epilogue
-                self.weight.grad = _gemm.linear_weight_grad(g2, x2, out=self.weight.grad)
+                # dW (+)= dYᵀ·X with the accumulation fused in the kernel epilogue.  On the
+                # step's last W pass of a data-parallel run the epilogue also pushes the
+                # finished gradient to the other replicas (elf_b200.parallel.dp_sync).
+                push = None
+                plan = getattr(self, "_push", None)
+                if plan is not None and getattr(self, "_final_pass", False) and self.weight.grad is not None and self.weight.grad.dtype == self.weight.dtype:
+                    push = plan.target()
+                self.weight.grad = _gemm.linear_weight_grad(g2, x2, out=self.weight.grad, push=push)
             else:
                 dw = torch.mm(g2.t(), x2.conj() if g2.is_complex() else x2)
                 if self.weight.grad is None:
