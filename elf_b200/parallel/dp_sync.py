@@ -118,6 +118,11 @@ class StageExchange:
 
     def finish_step(self, scale: float) -> None:
         """Push what the GEMM epilogues did not, then reduce.  Enqueues two kernels."""
+        self.push_rest()
+        self.reduce(scale)
+
+    def push_rest(self) -> None:
+        """Copy every range no GEMM epilogue pushed into the peers' inboxes and raise flag 0."""
         ext = _ext.get()
         dev = self.flat.device
         self.flat.gather_stray_grads()
@@ -132,6 +137,11 @@ class StageExchange:
         slots, flags = self._device_tables()
         rng = torch.tensor(ranges if ranges else [(0, 0)], dtype=torch.int64, device=dev)
         ext.push_ranges(self.flat.flat_grad, rng, slots, flags, self.epoch, self.counter)
+
+    def reduce(self, scale: float) -> None:
+        """Wait (bounded) for the peers' flags of this step, then ``grad = scale * (local + peers)``."""
+        ext = _ext.get()
+        dev = self.flat.device
         wait = torch.tensor([0] + sorted(self.pushed), dtype=torch.int32, device=dev)
         par = self.epoch & 1
         inbox = self.inbox.local[par * self.n_peers * self.numel : (par + 1) * self.n_peers * self.numel]

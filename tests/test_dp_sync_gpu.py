@@ -61,8 +61,10 @@ def test_fused_dw_push_and_finalize(world):
             grads = [p.grad.clone() for p in ref.parameters()]
             ref_grads = grads if ref_grads is None else [a + b for a, b in zip(ref_grads, grads)]
         scale = 1.0 / (n_mb * batch * world)
+        for ex in exchanges:  # all pushes first: on one GPU a finalize must not wait for a later launch
+            ex.push_rest()
         for ex in exchanges:
-            ex.finish_step(scale)
+            ex.reduce(scale)
         torch.cuda.synchronize()
         G.check_status()
         for m in reps:
