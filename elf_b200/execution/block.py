@@ -187,6 +187,10 @@ class PipelineBlock:
         outputs = [v[0].get(v[0].saved, mb_id) for v in self.output_variables]
         out_grads = []
         for var_dsts in self.output_variables:
+            for var in var_dsts:  # gradient channels learn their shape from the forward output
+                ch = var.recv_channel
+                if ch is not None and ch.direction == "bwd" and ch.metadata is None and var.metadata is not None:
+                    ch.set_metadata(var.metadata)
             g = var_dsts[0].wait_and_pop(mb_id)
             for other in var_dsts[1:]:
                 g = g + other.wait_and_pop(mb_id)

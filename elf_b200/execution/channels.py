@@ -21,6 +21,7 @@ the host on a peer that has not reached its send yet.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -63,13 +64,18 @@ class Channel:
         self.index = index
         self.n_channels = max(1, n_channels)
         self.metadata: Optional[TensorMetadata] = None
-        self.header_sent = False
+        # Only forward channels carry a header: a gradient has the shape of the activation
+        # that went the other way, which its receiver produced itself.
+        self.header_sent = direction == "bwd"
         self._header_work = None
         self._header_buf: Optional[torch.Tensor] = None
         self._deferred: List[Tuple[int, int]] = []  # (mb, batch) recvs posted before the shape was known
         self._posted: Dict[int, _Pending] = {}
         self._sends: List = []
-        self._tagged = dist.get_backend(group) != "nccl"
+        # NCCL matches sends and recvs of a communicator purely by order; gloo can use tags.
+        # ELF_B200_P2P_STRICT=1 makes gloo behave like NCCL (untagged, one group per channel)
+        # so that ordering or size mismatches show up in CPU tests.
+        self._tagged = dist.get_backend(group) != "nccl" and os.environ.get("ELF_B200_P2P_STRICT", "0") != "1"
 
     def _tag(self, mb: int, header: bool = False) -> int:
         if not self._tagged:
@@ -109,7 +115,7 @@ class Channel:
 
     def post_recv(self, mb: int, batch: int) -> None:
         if self.metadata is None:
-            if self._header_work is None:
+            if self._header_work is None and self.direction == "fwd":
                 self._header_buf = torch.zeros(TensorMetadata.MAX_SIZE, dtype=torch.int64, device=self.device)
                 self._header_work = dist.irecv(self._header_buf, src=self.peer, group=self.group, tag=self._tag(mb, True))
             self._deferred.append((mb, batch))
@@ -123,6 +129,8 @@ class Channel:
 
     def _resolve_header(self) -> None:
         if self.metadata is None:
+            if self._header_work is None:
+                raise RuntimeError(f"{self}: shape of the incoming tensor is unknown (set_metadata was never called)")
             self._header_work.wait()
             self.metadata = TensorMetadata.from_tensor(self._header_buf.cpu(), device=self.device)
             self._header_work = self._header_buf = None
@@ -161,7 +169,7 @@ class ChannelTable:
         self._groups = []
         backend = dist.get_backend(pp_group)
         if dedicated_groups is None:
-            dedicated_groups = backend == "nccl"
+            dedicated_groups = backend == "nccl" or os.environ.get("ELF_B200_P2P_STRICT", "0") == "1"
         # one channel per tensor crossing the edge: a channel carries one fixed shape
         edges = []
         for a, b in edge_list(signatures):

@@ -12,7 +12,7 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def launch(case: str, nproc: int, timeout: int = 600):
+def launch(case: str, nproc: int, timeout: int = 240):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(29600 + (os.getpid() % 300)), os.path.join(ROOT, "tests", "multigpu_worker.py"), case]

@@ -37,7 +37,11 @@ def _stage_param_names(model, n_stages):
     return names
 
 
-def _worker(rank, world, scheduler, placement, dp, nmb, split_w):
+def _worker(rank, world, scheduler, placement, dp, nmb, split_w, strict=False):
+    import os
+
+    if strict:
+        os.environ["ELF_B200_P2P_STRICT"] = "1"
     from elf_b200 import Pipeline, replace_layer_with_layer_dw
     from elf_b200.models.gpt import GPT, GPTConfig, gpt_stages
 
@@ -106,3 +110,10 @@ def test_pipeline_matches_single_process(scheduler, placement, dp, nmb, split_w)
 @pytest.mark.parametrize("scheduler,placement", [("1f1b", [0, 1]), ("zbv", [0, 1, 1, 0]), ("zbh1", [0, 1]), ("hanayo", [0, 1, 1, 0])])
 def test_data_parallel_replicas(scheduler, placement):
     run_ranks(_worker, 4, scheduler, placement, 2, 4, scheduler.startswith("zb"))
+
+
+@pytest.mark.parametrize("scheduler,placement,split_w", [("zbv", [0, 1, 1, 0], True), ("1f1b", [0, 1, 0, 1], False), ("zbh1", [0, 1], True)])
+def test_untagged_channels_like_nccl(scheduler, placement, split_w):
+    """One communicator per channel and no tags: messages are matched by order and size only,
+    as NCCL does, so a stray header or a misordered recv fails here instead of on GPUs."""
+    run_ranks(_worker, 2, scheduler, placement, 1, 4, split_w, True)
