@@ -26,6 +26,27 @@ NVCC_FLAGS = [
 ]
 
 
+NOALLOC_LIB = "libelfb_noalloc.so"
+
+
+def build_noalloc_library(verbose: bool = False) -> Path:
+    """Stand-alone shared library (no PyTorch dependency) with the allocation-free entry point
+    of ``rmsnorm_bwd_noalloc.h``; callers load it with ``dlopen`` / ``ctypes``."""
+    import subprocess
+
+    BUILD_DIR.mkdir(exist_ok=True)
+    out = BUILD_DIR / NOALLOC_LIB
+    srcs = [HERE / "rmsnorm_bwd_noalloc.cu", HERE / "fused_ops.cu"]
+    deps = srcs + [HERE / "rmsnorm_bwd_noalloc.h", HERE / "fused_ops.h"]
+    if out.exists() and all(out.stat().st_mtime >= d.stat().st_mtime for d in deps):
+        return out
+    cmd = ["nvcc", "-shared", "-Xcompiler", "-fPIC", *NVCC_FLAGS, "-cudart", "shared", "-o", str(out), *map(str, srcs)]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.run(cmd, check=True)
+    return out
+
+
 def sources():
     out = [str(HERE / s) for s in SOURCES]
     out += [str(HERE / s) for s in OPTIONAL_SOURCES if (HERE / s).exists()]
@@ -44,6 +65,7 @@ def build(verbose: bool = False):
         defines.append("-DELFB_WITH_ATTENTION")
     if (HERE / "dp_reduce.cu").exists():
         defines.append("-DELFB_WITH_DP_REDUCE")
+    build_noalloc_library(verbose)
     return cpp_extension.load(
         name=NAME,
         sources=sources(),
