@@ -34,6 +34,37 @@ _CONFIGS = {
 }
 
 
+def _layers_per_stage(c, placement):
+    """Layer counts balancing the work per RANK: the rank with the last stage also runs the LM
+    head, which costs `head` decoder layers.  (Same rule as the other arm of the benchmark,
+    restated here because this file imports nothing from it.)"""
+    n_layers, n_stages = c["n_layers"], len(placement)
+    d, hd = c["d_model"], c["d_model"] // c["n_heads"]
+    layer = 2 * d * (c["n_heads"] + 2 * c["n_kv_heads"]) * hd + 2 * d * d + 6 * d * c["ffn"] + 2 * c["seq_len"] * d
+    head = 2 * d * c["vocab"] / layer
+    ranks = sorted(set(placement))
+    stages_of = {r: [s for s in range(n_stages) if placement[s] == r] for r in ranks}
+    head_rank = placement[-1]
+    per_rank = {r: 0 for r in ranks}
+    if len(ranks) == 1:
+        per_rank[head_rank] = n_layers
+    else:
+        target = (n_layers + head) / len(ranks)
+        per_rank[head_rank] = max(len(stages_of[head_rank]) if n_layers >= n_stages else 0, int(round(target - head)))
+        others = [r for r in ranks if r != head_rank]
+        base, extra = divmod(n_layers - per_rank[head_rank], len(others))
+        for i, r in enumerate(others):
+            per_rank[r] = base + (1 if i < extra else 0)
+    counts = [0] * n_stages
+    for r in ranks:
+        st = stages_of[r]
+        base, extra = divmod(per_rank[r], len(st))
+        for i, s in enumerate(st):
+            counts[s] = base + (1 if i < extra else 0)
+    assert sum(counts) == n_layers
+    return counts
+
+
 def _unavailable(why: str) -> None:
     print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
@@ -145,8 +176,7 @@ def run_reference(args) -> None:
         return _unavailable(f"the reference's {scheduler} schedule is empty or raises IndexError on replicas other than the first (dp={args.dp})")
     placement = Placement.default(scheduler, pp)
     n_stages = len(placement)
-    base, extra = divmod(c["n_layers"], n_stages)
-    counts = [base + (1 if i < extra else 0) for i in range(n_stages)]
+    counts = _layers_per_stage(c, list(placement))
     RefLayer, RefEmbed, RefHead = _build_modules(torch, nn, F)
     mine = [i for i in range(n_stages) if placement[i] == rank % pp]
     parts = []
@@ -268,6 +298,7 @@ def run_reference(args) -> None:
             "parallelism": f"pp{pp}" + (f"xdp{args.dp}" if args.dp > 1 else ""),
             "scheduler": scheduler,
             "placement": list(placement),
+            "layers_per_stage": counts,
             "optimizer": "torch.optim.AdamW(fused=True) on bf16 parameters, step inside the timed region",
             "note": note,
         },

@@ -52,7 +52,7 @@ def run_ours(args):
 
     from benchmarks.benchmark_utils import ClockSampler, init_dist, max_over_ranks
     from elf_b200 import Pipeline, Placement
-    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, llama_loss_fn
+    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, head_cost_in_layers, layers_per_stage, llama_loss_fn
     from elf_b200.ops import _ext
     from elf_b200.optim import DummyOptimizer, FusedAdamW
     from dataclasses import replace
@@ -70,7 +70,7 @@ def run_ours(args):
     placement = Placement.default(args.scheduler, pp)
     pp_rank = rank % pp
     mine = placement.get_ids(pp_rank)
-    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234)
+    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement))
     parts = [stages[i] for i in mine]
     pipe = Pipeline(parts, None, partitioner=False, scheduler=args.scheduler, placement=list(placement), dp=dp, outputs="none")
     params = list(pipe.parameters())
@@ -167,6 +167,7 @@ def run_ours(args):
             "parallelism": f"pp{pp}" + (f"xdp{dp}" if dp > 1 else ""),
             "scheduler": args.scheduler,
             "placement": list(placement),
+            "layers_per_stage": layers_per_stage(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg)),
             "optimizer": "fused AdamW, fp32 master/m/v, step inside the timed region",
             "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed",
         },

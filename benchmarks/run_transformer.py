@@ -123,7 +123,7 @@ def main():
     if args.architecture == "llama":
         cfg = LLAMA_CONFIGS[args.model]
         mine = placement.get_ids(pp_rank)
-        stages = build_llama_stages(cfg, len(placement), only=mine, device=device, dtype=dtype, seed=1234)
+        stages = build_llama_stages(cfg, len(placement), only=mine, device=device, dtype=dtype, seed=1234, placement=list(placement))
         parts, signatures, partitioner = [stages[i] for i in mine], sequential_signatures(placement), False
         loss_fn, vocab, seq = llama_loss_fn, cfg.vocab, cfg.seq_len
         sample = torch.randint(0, vocab, (args.mb_size, seq), device=device)

@@ -42,6 +42,7 @@ __all__ = [
     "llama_loss_fn",
     "init_llama_",
     "layers_per_stage",
+    "head_cost_in_layers",
 ]
 
 
@@ -160,21 +161,57 @@ def init_llama_(module: nn.Module, std: float = 0.02, seed: Optional[int] = None
     return module
 
 
-def layers_per_stage(n_layers: int, n_stages: int) -> List[int]:
-    """Balanced decoder-layer counts.  The embedding costs almost nothing and the head
-    about one layer, so when the layers do not divide evenly the extra ones go to the
-    first stages."""
-    base, extra = divmod(n_layers, n_stages)
-    return [base + (1 if i < extra else 0) for i in range(n_stages)]
+def head_cost_in_layers(cfg: LlamaConfig) -> float:
+    """FLOPs of the LM head (final norm + vocabulary projection) in units of one decoder layer."""
+    d, hd = cfg.d_model, cfg.head_dim
+    layer = 2 * d * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + 2 * d * d + 6 * d * cfg.ffn + 2 * cfg.seq_len * d  # last term: causal attention
+    return 2 * d * cfg.vocab / layer
 
 
-def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True) -> List[Optional[LlamaStage]]:
+def layers_per_stage(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0) -> List[int]:
+    """Decoder-layer count of every stage.
+
+    Without a placement: as even as possible.  With one, the counts balance the work per
+    *rank*: the rank hosting the last stage also runs the LM head, which costs ``head_units``
+    layers (2.2 for the 8B shape with its 128k vocabulary), so it gets that many fewer layers.
+    With a V placement the first and the last stage share a rank, and ignoring this would make
+    that rank the bottleneck of the whole pipeline."""
+    if placement is None or len(set(placement)) == n_stages == 1:
+        base, extra = divmod(n_layers, n_stages)
+        return [base + (1 if i < extra else 0) for i in range(n_stages)]
+    assert len(placement) == n_stages
+    ranks = sorted(set(placement))
+    stages_of = {r: [s for s in range(n_stages) if placement[s] == r] for r in ranks}
+    head_rank = placement[-1]
+    target = (n_layers + head_units) / len(ranks)
+    per_rank = {r: 0 for r in ranks}
+    per_rank[head_rank] = max(len(stages_of[head_rank]) if n_layers >= n_stages else 0, int(round(target - head_units)))
+    others = [r for r in ranks if r != head_rank]
+    left = n_layers - per_rank[head_rank]
+    if others:
+        base, extra = divmod(left, len(others))
+        for i, r in enumerate(others):
+            per_rank[r] = base + (1 if i < extra else 0)
+    else:
+        per_rank[head_rank] = n_layers
+    counts = [0] * n_stages
+    for r in ranks:
+        st = stages_of[r]
+        base, extra = divmod(per_rank[r], len(st))
+        for i, s in enumerate(st):
+            counts[s] = base + (1 if i < extra else 0)
+    assert sum(counts) == n_layers, (counts, n_layers)
+    return counts
+
+
+def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None) -> List[Optional[LlamaStage]]:
     """Build the stages listed in ``only`` (all by default) directly on ``device``; the
     others are returned as ``None``, so a rank materialises only what it hosts.  Stage ``i``
-    is seeded with ``seed + i``: the weights of a stage do not depend on who builds it."""
+    is seeded with ``seed + i``: the weights of a stage do not depend on who builds it.
+    With ``placement`` the layer counts are balanced per rank (see ``layers_per_stage``)."""
     from ..zb_utils import replace_layer_with_layer_dw
 
-    counts = layers_per_stage(cfg.n_layers, n_stages)
+    counts = layers_per_stage(cfg.n_layers, n_stages, placement, head_cost_in_layers(cfg) if placement is not None else 0.0)
     stages: List[Optional[LlamaStage]] = []
     for i, n in enumerate(counts):
         if only is not None and i not in only:
