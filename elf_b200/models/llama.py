@@ -90,6 +90,8 @@ class RMSNorm(nn.Module):
 
 
 class LlamaEmbedding(nn.Module):
+    _elf_leaf = True  # one graph node for the tracers: partitioners cut between layers, not inside
+
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(cfg.vocab, cfg.d_model))
@@ -99,6 +101,8 @@ class LlamaEmbedding(nn.Module):
 
 
 class LlamaDecoderLayer(nn.Module):
+    _elf_leaf = True
+
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
         d, hd = cfg.d_model, cfg.head_dim
@@ -131,6 +135,8 @@ class LlamaDecoderLayer(nn.Module):
 
 
 class LlamaHead(nn.Module):
+    _elf_leaf = True
+
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.norm = RMSNorm(cfg.d_model, cfg.eps)

@@ -125,10 +125,13 @@ def create_subgraph(graph_module: fx.GraphModule, nodes: List[fx.Node], inputs: 
     sub = fx.Graph()
     env: Dict[str, fx.Node] = {}
     for name in inputs:
-        env[name] = sub.placeholder(name)
+        node = sub.placeholder(name)
+        env[name] = node
+        env[node.name] = node  # fx may rename (a placeholder called `input` becomes `input_1`)
     for nd in nodes:
         env[nd.name] = sub.node_copy(nd, lambda a: env[a.name])
     sub.output(tuple(env[o] for o in outputs))
+    sub.lint()
     return fx.GraphModule(graph_module, sub)
 
 

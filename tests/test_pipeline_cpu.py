@@ -117,3 +117,44 @@ def test_untagged_channels_like_nccl(scheduler, placement, split_w):
     """One communicator per channel and no tags: messages are matched by order and size only,
     as NCCL does, so a stray header or a misordered recv fails here instead of on GPUs."""
     run_ranks(_worker, 2, scheduler, placement, 1, 4, split_w, True)
+
+
+def _auto_worker(rank, world, partitioner, dp):
+    """Rank 0 traces, profiles and cuts the whole model; the other ranks receive their stages."""
+    import copy
+
+    from elf_b200 import Pipeline, replace_layer_with_layer_dw
+    from elf_b200.models.llama import LlamaConfig, build_llama, llama_loss_fn
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(n_layers=4, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=256, seq_len=32, rope_theta=10000.0)
+    model = build_llama(cfg, dtype=torch.float32, seed=3)
+    ref = copy.deepcopy(model)
+    replace_layer_with_layer_dw(model)
+    pp = world // dp
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, cfg.vocab, (dp * 4, cfg.seq_len + 1), generator=g)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    pipe = Pipeline(model, ids[:1], partitioner=partitioner, scheduler="1f1b", dp=dp, outputs="device")
+    assert len(pipe.signatures) == pp and len(pipe.blocks) == 1
+    lo = (rank // pp) * 4
+    out, loss = pipe(ids[lo : lo + 4], tgt[lo : lo + 4], llama_loss_fn, split_size=1)
+    ref_loss = llama_loss_fn(ref(ids), tgt)
+    ref_loss.backward()
+    if pipe.is_last():
+        torch.testing.assert_close(loss, ref_loss.detach(), atol=ATOL, rtol=RTOL)
+    ref_grads = dict(ref.named_parameters())
+    seen = 0
+    for name, p in pipe.named_parameters():  # fx sub-modules keep the original qualified names
+        torch.testing.assert_close(p.grad, ref_grads[name].grad, atol=ATOL, rtol=RTOL, msg=lambda m: f"{name}: {m}")
+        seen += 1
+    assert seen > 0
+    merged = pipe.gather_parameters(dst=(rank // pp) * pp)
+    if rank % pp == 0:
+        assert set(merged) == set(ref_grads)
+    pipe.clear()
+
+
+@pytest.mark.parametrize("partitioner,world,dp", [("constrained", 2, 1), ("naive", 2, 1), ("dagP", 4, 2)])
+def test_auto_partition_and_model_shipping(partitioner, world, dp):
+    run_ranks(_auto_worker, world, partitioner, dp)
