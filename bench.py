@@ -72,7 +72,20 @@ def run_ours(args):
     mine = placement.get_ids(pp_rank)
     stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement))
     parts = [stages[i] for i in mine]
-    pipe = Pipeline(parts, None, partitioner=False, scheduler=args.scheduler, placement=list(placement), dp=dp, outputs="none")
+    counts = layers_per_stage(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg))
+    scheduler, sched_note = args.scheduler, args.scheduler
+    if args.scheduler == "zbv" and pp > 1:
+        # ZB-V laid out for what the stages cost: layer counts differ per stage, the last stage
+        # also runs the LM head, and B is longer than F and W (attention backward).  Up to 3p
+        # live (stage, micro-batch) activations per rank instead of 2p: memory is not scarce here.
+        import functools
+
+        from elf_b200.scheduling.schedulers import generate_zbv_schedule
+
+        stage_costs = [c + (head_cost_in_layers(cfg) if i == len(placement) - 1 else 0.0) for i, c in enumerate(counts)]
+        scheduler = functools.partial(generate_zbv_schedule, cap=3 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
+        sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, at most 3p live activations per rank)"
+    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none")
     params = list(pipe.parameters())
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()
 
@@ -165,9 +178,9 @@ def run_ours(args):
             "micro_batch_size": args.mb_size,
             "seq_len": cfg.seq_len,
             "parallelism": f"pp{pp}" + (f"xdp{dp}" if dp > 1 else ""),
-            "scheduler": args.scheduler,
+            "scheduler": sched_note,
             "placement": list(placement),
-            "layers_per_stage": layers_per_stage(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg)),
+            "layers_per_stage": counts,
             "optimizer": "fused AdamW, fp32 master/m/v, step inside the timed region",
             "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed",
         },

@@ -280,23 +280,28 @@ def _list_schedule(
     *,
     split_w: bool,
     cap: Dict[int, int] | int | None = None,
-    cost_f: int = 1,
-    cost_b: int = 1,
-    cost_w: int = 1,
-    hop: int = 0,
+    cost_f: float = 1,
+    cost_b: float = 1,
+    cost_w: float = 1,
+    hop: float = 0,
+    stage_costs: Optional[Sequence[float]] = None,
 ) -> List[Operation]:
-    """Greedy unit-time simulation of the whole pipeline.
+    """Greedy event-driven simulation of the whole pipeline.
 
-    At every tick each idle rank starts, in this order of preference,
+    Whenever a rank becomes idle it starts, in this order of preference,
     (1) the oldest ready backward-inputs (ready = own forward done and the next stage's B
-        done, ``hop`` ticks earlier when that stage is on another rank);
+        done, ``hop`` later when that stage is on another rank);
     (2) the deepest ready forward, if the rank holds fewer than ``cap`` live
         (stage, micro-batch) activations (live = forwarded, W not yet run);
     (3) the oldest pending backward-params (only when ``split_w``; otherwise W is glued
-        to its B).
-    If the cap ever starves the whole pipeline it is lifted by one on the blocked ranks.
-    Because the result is read off a feasible timeline, the per-rank programs admit a
-    global order and cannot deadlock once comms are added.
+        to its B);
+    otherwise it idles until the next completion anywhere in the pipeline.  An op of stage
+    ``s`` lasts ``stage_costs[s]`` (default 1) times ``cost_f`` / ``cost_b`` / ``cost_w``, so
+    stages of unequal weight (more layers, the LM head) and F/B/W of unequal length are
+    scheduled for what they cost rather than as unit slots.  If the cap ever starves the
+    whole pipeline it is lifted by one on the blocked ranks.  Because the result is read
+    off a feasible timeline, the per-rank programs admit a global order and cannot
+    deadlock once comms are added.
     """
     n_stages = len(placement)
     by_rank = _stages_by_rank(placement)
@@ -306,103 +311,110 @@ def _list_schedule(
     elif isinstance(cap, int):
         cap = {r: cap for r in ranks}
     cap = dict(cap)
+    weight = [1.0] * n_stages if stage_costs is None else [float(c) for c in stage_costs]
+    assert len(weight) == n_stages, "one cost per stage"
 
-    UNSET = -1
-    f_end = [[UNSET] * n for _ in range(n_stages)]
-    b_end = [[UNSET] * n for _ in range(n_stages)]
+    UNSET = None
+    f_end: List[List[Optional[float]]] = [[UNSET] * n for _ in range(n_stages)]
+    b_end: List[List[Optional[float]]] = [[UNSET] * n for _ in range(n_stages)]
     f_next = [0] * n_stages
     b_next = [0] * n_stages
     w_next = [0] * n_stages
-    busy_until = {r: 0 for r in ranks}
+    free_at = {r: 0.0 for r in ranks}
     out = _Programs(placement)
     total = n_stages * n * 3
     done = 0
-    t = 0
-    idle_ticks = 0
+    EPS = 1e-9
 
-    def arrival(end: int, src_stage: int, dst_stage: int) -> int:
+    def arrival(end: float, src_stage: int, dst_stage: int) -> float:
         return end + (hop if placement[src_stage] != placement[dst_stage] else 0)
 
-    def f_ready(s: int) -> bool:
+    def f_ready_at(s: int) -> Optional[float]:
+        """Time from which the next forward of stage ``s`` may start (None: not yet known)."""
         mb = f_next[s]
         if mb >= n:
-            return False
+            return None
         if s == 0:
-            return True
+            return 0.0
         e = f_end[s - 1][mb]
-        return e != UNSET and arrival(e, s - 1, s) <= t
+        return None if e is UNSET else arrival(e, s - 1, s)
 
-    def b_ready(s: int) -> bool:
+    def b_ready_at(s: int) -> Optional[float]:
         mb = b_next[s]
-        if mb >= n or f_end[s][mb] == UNSET or f_end[s][mb] > t:
-            return False
+        if mb >= n or f_end[s][mb] is UNSET:
+            return None
+        t0 = f_end[s][mb]
         if s == n_stages - 1:
-            return True
+            return t0
         e = b_end[s + 1][mb]
-        return e != UNSET and arrival(e, s + 1, s) <= t
+        return None if e is UNSET else max(t0, arrival(e, s + 1, s))
 
     def live(rank: int) -> int:
         return sum(f_next[s] - w_next[s] for s in by_rank[rank])
 
+    stalled_rounds = 0
     while done < total:
-        progressed = False
-        blocked_by_cap = []
-        for r in ranks:
-            if busy_until[r] > t:
-                progressed = True
-                continue
-            stages = by_rank[r]
-            cand_b = [s for s in stages if b_ready(s)]
-            if cand_b:
-                s = min(cand_b, key=lambda s: (b_next[s], s))
-                mb = b_next[s]
-                out.B(s, mb)
-                b_next[s] += 1
-                dur = cost_b
+        r = min(ranks, key=lambda q: (free_at[q], q))
+        t = free_at[r]
+        stages = by_rank[r]
+        b_times = {s: b_ready_at(s) for s in stages}
+        cand_b = [s for s in stages if b_times[s] is not None and b_times[s] <= t + EPS]
+        if cand_b:
+            s = min(cand_b, key=lambda s: (b_next[s], s))
+            mb = b_next[s]
+            out.B(s, mb)
+            b_next[s] += 1
+            dur = cost_b * weight[s]
+            done += 1
+            b_end[s][mb] = t + dur
+            if not split_w:
+                out.W(s, mb)
+                w_next[s] += 1
+                dur += cost_w * weight[s]
                 done += 1
-                if not split_w:
-                    out.W(s, mb)
-                    w_next[s] += 1
-                    dur += cost_w
-                    done += 1
-                b_end[s][mb] = t + cost_b
-                busy_until[r] = t + dur
-                progressed = True
+            free_at[r] = t + dur
+            stalled_rounds = 0
+            continue
+        f_times = {s: f_ready_at(s) for s in stages}
+        cand_f = [s for s in stages if f_times[s] is not None and f_times[s] <= t + EPS]
+        capped = bool(cand_f) and live(r) >= cap[r]
+        if cand_f and not capped:
+            s = max(cand_f, key=lambda s: (s, -f_next[s]))
+            mb = f_next[s]
+            out.F(s, mb)
+            f_next[s] += 1
+            f_end[s][mb] = t + cost_f * weight[s]
+            free_at[r] = f_end[s][mb]
+            done += 1
+            stalled_rounds = 0
+            continue
+        if split_w:
+            cand_w = [s for s in stages if w_next[s] < b_next[s]]
+            if cand_w:
+                s = min(cand_w, key=lambda s: (w_next[s], s))
+                out.W(s, w_next[s])
+                w_next[s] += 1
+                free_at[r] = t + cost_w * weight[s]
+                done += 1
+                stalled_rounds = 0
                 continue
-            cand_f = [s for s in stages if f_ready(s)]
-            if cand_f:
-                if live(r) < cap[r]:
-                    s = max(cand_f, key=lambda s: (s, -f_next[s]))
-                    mb = f_next[s]
-                    out.F(s, mb)
-                    f_next[s] += 1
-                    f_end[s][mb] = t + cost_f
-                    busy_until[r] = t + cost_f
-                    done += 1
-                    progressed = True
-                    continue
-                blocked_by_cap.append(r)
-            if split_w:
-                cand_w = [s for s in stages if w_next[s] < b_next[s]]
-                if cand_w:
-                    s = min(cand_w, key=lambda s: (w_next[s], s))
-                    out.W(s, w_next[s])
-                    w_next[s] += 1
-                    busy_until[r] = t + cost_w
-                    done += 1
-                    progressed = True
-                    continue
-        if progressed:
-            idle_ticks = 0
-        else:
-            idle_ticks += 1
-            if idle_ticks > hop + 1:
-                if not blocked_by_cap:
+        # nothing to do now: sleep until something this rank waits for can have happened
+        known = [x for x in list(b_times.values()) + ([] if capped else list(f_times.values())) if x is not None and x > t + EPS]
+        others = [free_at[q] for q in ranks if q != r and free_at[q] > t + EPS]
+        wake = min(known + others) if (known or others) else None
+        if wake is None:
+            # every rank is idle at time t and nothing is in flight
+            stalled_rounds += 1
+            if stalled_rounds > len(ranks):
+                blocked = [q for q in ranks if live(q) >= cap[q] and any(f_ready_at(s) is not None for s in by_rank[q])]
+                if not blocked:
                     raise RuntimeError("list scheduler stalled: placement admits no feasible order")
-                for r in blocked_by_cap:
-                    cap[r] += 1
-                idle_ticks = 0
-        t += 1
+                for q in blocked:
+                    cap[q] += 1
+                stalled_rounds = 0
+            free_at[r] = t + EPS * 10  # let the other idle ranks be examined
+        else:
+            free_at[r] = wake
     return out.flat()
 
 
@@ -414,11 +426,17 @@ def generate_hanayo_schedule(placement, n_micro_batches) -> List[Operation]:
     return _list_schedule(placement, n_micro_batches, split_w=False, cap=max(1, len(placement) // p) * p)
 
 
-def generate_zbv_schedule(placement, n_micro_batches, *, cap: Optional[int] = None) -> List[Operation]:
+def generate_zbv_schedule(placement, n_micro_batches, *, cap: Optional[int] = None, stage_costs: Optional[Sequence[float]] = None,
+                          ratios: Sequence[float] = (1.0, 1.0, 1.0)) -> List[Operation]:
     """ZB-V on the V placement ``[0..p-1, p-1..0]`` for any number of micro-batches.  Each
     rank holds at most ``2p`` live (stage, micro-batch) activations — the footprint of
-    1F1B — and weight-gradient passes fill what would otherwise be bubbles."""
+    1F1B — and weight-gradient passes fill what would otherwise be bubbles.
+    ``stage_costs`` (relative weight of every stage) and ``ratios`` (F : B : W durations)
+    let the schedule be laid out for stages of unequal weight; use
+    ``functools.partial(generate_zbv_schedule, stage_costs=...)`` as the scheduler."""
     p = len(set(placement))
     if len(placement) != 2 * p:
         logger.warning("zbv expects a V placement with two stages per rank, got %s", list(placement))
-    return _list_schedule(placement, n_micro_batches, split_w=True, cap=cap if cap is not None else 2 * p)
+    cf, cb, cw = ratios
+    return _list_schedule(placement, n_micro_batches, split_w=True, cap=cap if cap is not None else 2 * p, cost_f=cf, cost_b=cb, cost_w=cw,
+                          stage_costs=stage_costs)

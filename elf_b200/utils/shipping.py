@@ -44,9 +44,10 @@ def _owner(model: nn.Module, qualified: str) -> Tuple[nn.Module, str]:
 
 
 def _named_tensors(model: nn.Module) -> List[Tuple[str, str, torch.Tensor]]:
-    """``(kind, qualified name, tensor)`` with shared tensors listed once per name."""
-    out = [("param", n, p) for n, p in model.named_parameters(remove_duplicate=False)]
-    out += [("buffer", n, b) for n, b in model.named_buffers(remove_duplicate=False)]
+    """``(kind, qualified name, tensor)``; a tensor reachable under several names (a module
+    used twice) is listed once - the pickled skeleton keeps the sharing."""
+    out = [("param", n, p) for n, p in model.named_parameters()]
+    out += [("buffer", n, b) for n, b in model.named_buffers()]
     return out
 
 
@@ -64,7 +65,7 @@ def _as_skeleton(model: nn.Module):
             table[leaf] = nn.Parameter(ghost, requires_grad=t.requires_grad) if kind == "param" else ghost
         yield model
     finally:
-        for table, leaf, original in undo:
+        for table, leaf, original in reversed(undo):
             table[leaf] = original
 
 
