@@ -336,6 +336,23 @@ const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t ro
   return msg;
 }
 
+// Row-major [rows][cols] output matrix of 16-bit (fmt 0/1) or fp32 (fmt 2) elements for TMA
+// stores / add-reductions: 128-byte swizzled boxes of box_cols x box_rows.
+const char* make_tmap_out(CUtensorMap* out, const void* ptr, int fmt, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                          uint32_t box_rows) {
+  EncodeFn enc = get_encode_fn();
+  if (!enc) return "cuTensorMapEncodeTiled entry point not found";
+  const uint64_t esz = fmt == 2 ? 4 : 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * esz};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = fmt == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed for the output matrix";
+}
+
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, void* d, const void* bias, int M, int N, int K,
                               long long ldd, uint32_t fmt, float alpha, int max_split, int* status, const PushTarget& push, int num_sms, cudaStream_t stream) {

@@ -19,6 +19,7 @@
 // cta_group::2 forms by warp 1 of both CTAs.
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "sm100_ptx.cuh"
 #include "gemm_epilogue.cuh"
@@ -40,7 +41,8 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 4;  // in units of 256-row pair tiles
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 + 256;
+constexpr int STAGING_BYTES = 2 * 16384;  // two 128-row x 128-byte chunks for the TMA-store epilogue
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
 
 struct WorkUnit {
   int m, n0, width;
@@ -92,12 +94,13 @@ template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
-                         void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
+                         const __grid_constant__ CUtensorMap tmap_d, void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
                          uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + size_t(STAGES) * STAGE_BYTES);
+  const uint32_t staging_base = smem_base + STAGES * STAGE_BYTES;  // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + size_t(STAGES) * STAGE_BYTES + STAGING_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -112,6 +115,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const bool leader = cta == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  const int dbg = max_split >> 8;
+  max_split &= 0xff;
   const Schedule sched = make_schedule(M, N, num_pairs, max_split);
   const int num_units = sched.total_units;
   const int k_blocks = (K + BK - 1) / BK;
@@ -161,6 +166,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint32_t bar = map_to_cta(full_bar(stage), 0);  // the leader's barrier
+          if (dbg & 2) {  // TEMP: no loads at all, MMA runs on whatever is in shared memory
+            if (leader) mbar_arrive(full_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if (leader) mbar_arrive_expect_tx(full_bar(stage), pair_tx);
           const int k0 = kb * BK;
           if (A_MN) {
@@ -231,25 +241,103 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
+    // Two paths.  With a push target (once per step and matrix) every thread stores its row
+    // straight to local and peer memory.  Otherwise the tile leaves through shared memory:
+    // each thread converts its row of a 128-byte-wide column chunk into a swizzled staging
+    // buffer and one thread hands the chunk to TMA (store, or add-reduce in L2 when
+    // accumulating), so the LSU issues no global stores and D is written in full lines.
     const int quarter = warp & 3;
+    const int ep_tid = threadIdx.x - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t leader_acc_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
+    const bool direct = push.n_peers > 0 || (dbg & 4);
+    constexpr int CHUNK_COLS = OUT_F32 ? 32 : 64;  // 128 bytes of output per row
+    int chunk_counter = 0;
     for (int unit = pair_id; unit < num_units; unit += num_pairs) {
       const WorkUnit wu = work_unit(unit, sched);
-      const int row = wu.m * (2 * BM) + int(cta) * BM + quarter * 32 + lane;
+      const int row0 = wu.m * (2 * BM) + int(cta) * BM;
+      const int row = row0 + quarter * 32 + lane;
       const int n0 = wu.n0;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      if (direct) {
 #pragma unroll 1
-      for (int c = 0; c < wu.width / 32; ++c) {
-        const int col = n0 + c * 32;
-        if (col >= N) break;
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha, push);
+        for (int c = 0; c < wu.width / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= N) break;
+          if (dbg & 1) continue;  // TEMP: skip the epilogue work
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha, push);
+        }
+      } else {
+        const int r_local = quarter * 32 + lane;          // row inside this CTA's 128-row slab
+        const uint32_t swz = uint32_t(r_local & 7);
+#pragma unroll 1
+        for (int c = 0; c < wu.width / CHUNK_COLS; ++c) {
+          const int col = n0 + c * CHUNK_COLS;
+          if (col >= N) break;
+          const uint32_t buf = staging_base + uint32_t(chunk_counter & 1) * 16384u;
+          // the chunk that used this buffer two chunks ago must have been read out by TMA
+          if (ep_tid == 0) tma_store_wait_read<1>();
+          named_barrier_sync(1, 128);
+          const uint32_t row_base = buf + uint32_t(r_local) * 128u;
+#pragma unroll
+          for (int h = 0; h < CHUNK_COLS / 32; ++h) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + c * CHUNK_COLS + h * 32, v);
+            tmem_ld_wait();
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * alpha;
+            if (BIAS) {
+              if (OUT_F32) {
+                const float* b = reinterpret_cast<const float*>(bias_ptr) + col + h * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] += (col + h * 32 + j < N) ? b[j] : 0.f;
+              } else {
+                const uint16_t* b = reinterpret_cast<const uint16_t*>(bias_ptr) + col + h * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const uint16_t hb = (col + h * 32 + j < N) ? b[j] : uint16_t(0);
+                  f[j] += fmt == 1u ? __bfloat162float(__ushort_as_bfloat16(hb)) : __half2float(__ushort_as_half(hb));
+                }
+              }
+            }
+            if (OUT_F32) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {  // eight 16-byte vectors = the whole 128-byte row
+                const uint32_t dst = row_base + ((uint32_t(q) ^ swz) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(f[4 * q]), "f"(f[4 * q + 1]), "f"(f[4 * q + 2]), "f"(f[4 * q + 3]) : "memory");
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {  // four 16-byte vectors = this half of the row
+                uint32_t p0, p1, p2, p3;
+                if (fmt == 1u) {
+                  p0 = pack_bf16x2(f[8 * q], f[8 * q + 1]); p1 = pack_bf16x2(f[8 * q + 2], f[8 * q + 3]);
+                  p2 = pack_bf16x2(f[8 * q + 4], f[8 * q + 5]); p3 = pack_bf16x2(f[8 * q + 6], f[8 * q + 7]);
+                } else {
+                  p0 = pack_f16x2(f[8 * q], f[8 * q + 1]); p1 = pack_f16x2(f[8 * q + 2], f[8 * q + 3]);
+                  p2 = pack_f16x2(f[8 * q + 4], f[8 * q + 5]); p3 = pack_f16x2(f[8 * q + 6], f[8 * q + 7]);
+                }
+                const uint32_t dst = row_base + ((uint32_t(h * 4 + q) ^ swz) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (ep_tid == 0) {
+            if (ACCUM) tma_reduce_add_2d(&tmap_d, buf, col, row0);
+            else tma_store_2d(&tmap_d, buf, col, row0);
+            tma_store_commit();
+          }
+          ++chunk_counter;
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -259,6 +347,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         acc_phase ^= 1u;
       }
     }
+    if (!direct && ep_tid == 0) tma_store_wait_all();  // every store of this CTA has landed
   }
 
   // ------------------------------------------------------------------ common exit
@@ -289,9 +378,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
 const char* make_tmap_2d(CUtensorMap* out, const void* ptr, int fmt, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
                          uint32_t box_rows);
+const char* make_tmap_out(CUtensorMap* out, const void* ptr, int fmt, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                          uint32_t box_rows);
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
-static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, const GemmArgs& g,
+static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, const CUtensorMap& td, const GemmArgs& g,
                                int num_sms, cudaStream_t stream) {
   using namespace pair;
   auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
@@ -304,16 +395,18 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
-  const int max_split = !g.split_tail ? 1 : (g.b_mn_major ? 2 : 4);  // MN-major B is fetched in 64-wide boxes per CTA
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha,
+  int max_split = !g.split_tail ? 1 : (g.b_mn_major ? 2 : 4);
+  static const int dbg = getenv("ELF_B200_GEMM_DEBUG") ? atoi(getenv("ELF_B200_GEMM_DEBUG")) : 0;  // TEMP experiment switch
+  max_split |= dbg << 8;  // MN-major B is fetched in 64-wide boxes per CTA
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha,
                                                        max_split, g.status, g.push);
   return cudaGetLastError();
 }
 
 template <bool A_MN, bool B_MN>
 static cudaError_t dispatch_pair(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
-                                 int num_sms, cudaStream_t s) {
-#define ELFB_LAUNCH(F32, ACC, BI) return launch_pair<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, g, num_sms, s)
+                                 const CUtensorMap& td, int num_sms, cudaStream_t s) {
+#define ELFB_LAUNCH(F32, ACC, BI) return launch_pair<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, td, g, num_sms, s)
   if (g.out_f32) {
     if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
     else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }
@@ -348,11 +441,15 @@ const char* gemm_tcgen05_pair(const GemmArgs& g, int num_sms, cudaStream_t strea
   }
   const int esz = g.out_f32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(g.d) & 15) != 0 || (g.ldd * esz) % 16 != 0) return "GEMM output must be 16-byte aligned with a 16-byte multiple row pitch";
+  // output map for the TMA-store epilogue: 128-byte-wide, 128-row boxes
+  CUtensorMap td;
+  err = make_tmap_out(&td, g.d, g.out_f32 ? 2 : g.fmt, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldd, g.out_f32 ? 32 : 64, BM);
+  if (err) return err;
   cudaError_t e;
-  if (g.a_mn_major && g.b_mn_major) e = dispatch_pair<true, true>(g, ta, tb, tb2, tb4, num_sms, stream);
-  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_pair<false, true>(g, ta, tb, tb2, tb4, num_sms, stream);
-  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_pair<false, false>(g, ta, tb, tb2, tb4, num_sms, stream);
-  else e = dispatch_pair<true, false>(g, ta, tb, tb2, tb4, num_sms, stream);
+  if (g.a_mn_major && g.b_mn_major) e = dispatch_pair<true, true>(g, ta, tb, tb2, tb4, td, num_sms, stream);
+  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_pair<false, true>(g, ta, tb, tb2, tb4, td, num_sms, stream);
+  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_pair<false, false>(g, ta, tb, tb2, tb4, td, num_sms, stream);
+  else e = dispatch_pair<true, false>(g, ta, tb, tb2, tb4, td, num_sms, stream);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
