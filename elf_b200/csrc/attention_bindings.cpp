@@ -1,0 +1,39 @@
+// torch glue for attention_sm100.cu.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "attention_sm100.h"
+
+namespace {
+
+// qkv: bf16 [B, S, Hq + 2 Hkv, 128] contiguous; out: bf16 [B, S, Hq, 128]; lse: fp32 [B, Hq, S]
+void attention_fwd(const at::Tensor& qkv, at::Tensor& out, at::Tensor& lse, int64_t n_heads, int64_t n_kv_heads, double scale,
+                   const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.is_contiguous() && qkv.dim() == 4, "qkv must be contiguous CUDA bf16 [B,S,H,128]");
+  TORCH_CHECK(qkv.size(3) == 128 && qkv.size(2) == n_heads + 2 * n_kv_heads, "qkv must hold Hq + 2 Hkv heads of 128");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() == qkv.size(0) * qkv.size(1) * n_heads * 128,
+              "out must be contiguous CUDA bf16 [B,S,Hq,128]");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == qkv.size(0) * n_heads * qkv.size(1),
+              "lse must be contiguous CUDA fp32 [B,Hq,S]");
+  c10::cuda::CUDAGuard g(qkv.device());
+  elfb::AttnArgs a;
+  a.qkv = qkv.data_ptr();
+  a.out = out.data_ptr();
+  a.lse = lse.data_ptr<float>();
+  a.batch = (int)qkv.size(0);
+  a.seq = (int)qkv.size(1);
+  a.n_heads = (int)n_heads;
+  a.n_kv_heads = (int)n_kv_heads;
+  a.scale = (float)scale;
+  a.status = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+  const char* err = elfb::attention_forward(a, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(err == nullptr, "elf_b200 attention: ", err ? err : "");
+}
+
+}  // namespace
+
+void register_attention(pybind11::module_& m) {
+  m.def("attention_fwd", &attention_fwd, "causal GQA flash attention forward (tcgen05), head_dim 128", py::arg("qkv"), py::arg("out"), py::arg("lse"),
+        py::arg("n_heads"), py::arg("n_kv_heads"), py::arg("scale") = 0.0, py::arg("status") = c10::nullopt);
+}

@@ -81,6 +81,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const c10::op
 void register_fused_ops(pybind11::module_& m);
 void register_host_runtime(pybind11::module_& m);
 void register_dp_reduce(pybind11::module_& m);
+void register_attention(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM: d (+)= alpha * a.b (+ bias)", py::arg("a"), py::arg("b"), py::arg("d"),
@@ -90,6 +91,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("push_flag_value") = 0, py::arg("push_counter") = c10::nullopt);
 #ifdef ELFB_WITH_DP_REDUCE
   register_dp_reduce(m);
+#endif
+#ifdef ELFB_WITH_ATTENTION
+  register_attention(m);
 #endif
   register_fused_ops(m);
   register_host_runtime(m);

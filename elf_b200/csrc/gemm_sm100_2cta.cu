@@ -45,55 +45,80 @@ constexpr int STAGING_BYTES = 2 * 16384;  // two 128-row x 128-byte chunks for t
 constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
 
 struct WorkUnit {
-  int m, n0, width;
+  int m, n0;      // tile row (in 256-row units) and first output column
+  int kb0, kb1;   // range of 64-wide k-blocks this unit contracts over
+  int part;       // index of this unit among the k-parts of its tile (0 when the tile is whole)
+  bool partial;   // true: the unit holds a partial sum and must add it to D
 };
+// Tiles are dealt round-robin to the CTA pairs.  When the tile count is not a multiple of
+// the pair count the last, partly filled wave would cost a whole tile time with most SMs
+// idle; instead each tile of that wave is split along K into `ksplit` units that run on
+// different pairs and add their partial sums to D (TMA add-reduce in L2).  Unlike a split
+// along N this keeps the 256x256 tile's ratio of MMA work to bytes loaded.
 struct Schedule {
-  int tiles_m, tiles_n, full_tiles, split, total_units;
+  int tiles_m, tiles_n, full_tiles, ksplit, total_units;
 };
 
-__host__ __device__ inline Schedule make_schedule(int M, int N, int num_pairs, int max_split) {
+__host__ __device__ inline Schedule make_schedule(int M, int N, int k_blocks, int num_pairs, int max_split) {
   Schedule s;
   s.tiles_m = (M + 2 * BM - 1) / (2 * BM);
   s.tiles_n = (N + BN - 1) / BN;
   const int tiles = s.tiles_m * s.tiles_n;
   const int rem = tiles % num_pairs;
-  s.split = 1;
+  s.ksplit = 1;
   if (rem != 0 && tiles > rem) {
-    int best_num = 1, best_den = 1;
-    for (int f = 2; f <= max_split; f *= 2) {
+    // cost of the last wave in 1/840 tile times, plus a charge per extra part for its exposed epilogue
+    int best = 840;
+    for (int f = 2; f <= max_split && f * 4 <= k_blocks; ++f) {
       const int waves = (rem * f + num_pairs - 1) / num_pairs;
-      if (waves * best_den < best_num * f) {
-        best_num = waves;
-        best_den = f;
-        s.split = f;
+      const int cost = waves * 840 / f + 30 * (f - 1);
+      if (cost < best) {
+        best = cost;
+        s.ksplit = f;
       }
     }
   }
-  s.full_tiles = s.split == 1 ? tiles : tiles - rem;
-  s.total_units = s.full_tiles + (tiles - s.full_tiles) * s.split;
+  s.full_tiles = s.ksplit == 1 ? tiles : tiles - rem;
+  s.total_units = s.full_tiles + (tiles - s.full_tiles) * s.ksplit;
   return s;
 }
 
-__device__ __forceinline__ WorkUnit work_unit(int unit, const Schedule& s) {
-  int tile = unit, strip = 0, width = BN;
-  if (unit >= s.full_tiles) {
-    const int u = unit - s.full_tiles;
-    tile = s.full_tiles + u / s.split;
-    strip = u % s.split;
-    width = BN / s.split;
-  }
+__host__ __device__ inline void tile_coords(int tile, const Schedule& s, int* m, int* n) {
   const int per_group = GROUP_M * s.tiles_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
-  const int rows = min(GROUP_M, s.tiles_m - first_m);
+  const int rows = (s.tiles_m - first_m) < GROUP_M ? (s.tiles_m - first_m) : GROUP_M;
   const int in_group = tile - group * per_group;
-  return {first_m + in_group % rows, (in_group / rows) * BN + strip * width, width};
+  *m = first_m + in_group % rows;
+  *n = in_group / rows;
+}
+
+__device__ __forceinline__ WorkUnit work_unit(int unit, const Schedule& s, int k_blocks) {
+  WorkUnit wu;
+  int tile = unit;
+  wu.kb0 = 0;
+  wu.kb1 = k_blocks;
+  wu.part = 0;
+  wu.partial = false;
+  if (unit >= s.full_tiles) {
+    // parts of one tile are `rem` units apart, so they land on different pairs
+    const int rem = (s.total_units - s.full_tiles) / s.ksplit;
+    const int u = unit - s.full_tiles;
+    tile = s.full_tiles + u % rem;
+    wu.part = u / rem;
+    wu.kb0 = int((long long)k_blocks * wu.part / s.ksplit);
+    wu.kb1 = int((long long)k_blocks * (wu.part + 1) / s.ksplit);
+    wu.partial = true;
+  }
+  int n;
+  tile_coords(tile, s, &wu.m, &n);
+  wu.n0 = n * BN;
+  return wu;
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_b_quarter,
                          const __grid_constant__ CUtensorMap tmap_d, void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
                          uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push) {
   extern __shared__ uint8_t smem_raw[];
@@ -115,11 +140,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const bool leader = cta == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int dbg = max_split >> 8;
-  max_split &= 0xff;
-  const Schedule sched = make_schedule(M, N, num_pairs, max_split);
-  const int num_units = sched.total_units;
   const int k_blocks = (K + BK - 1) / BK;
+  const Schedule sched = make_schedule(M, N, k_blocks, num_pairs, max_split);
+  const int num_units = sched.total_units;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -152,13 +175,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       for (int unit = pair_id; unit < num_units && ok; unit += num_pairs) {
-        const WorkUnit wu = work_unit(unit, sched);
+        const WorkUnit wu = work_unit(unit, sched, k_blocks);
         const int m0 = wu.m * (2 * BM) + int(cta) * BM;  // this CTA's 128 rows
-        const int half = wu.width / 2;
+        constexpr int half = BN / 2;
         const int n0 = wu.n0 + int(cta) * half;          // this CTA's half of the B rows
-        const uint32_t pair_tx = 2u * (A_BYTES + half * BK * 2);
-        const CUtensorMap* tb_k = wu.width == BN ? &tmap_b : (wu.width == BN / 2 ? &tmap_b_half : &tmap_b_quarter);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        constexpr uint32_t pair_tx = 2u * (A_BYTES + B_BYTES);
+        for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -166,11 +188,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint32_t bar = map_to_cta(full_bar(stage), 0);  // the leader's barrier
-          if (dbg & 2) {  // TEMP: no loads at all, MMA runs on whatever is in shared memory
-            if (leader) mbar_arrive(full_bar(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-            continue;
-          }
           if (leader) mbar_arrive_expect_tx(full_bar(stage), pair_tx);
           const int k0 = kb * BK;
           if (A_MN) {
@@ -180,9 +197,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
           }
           if (B_MN) {
+#pragma unroll
             for (int j = 0; j < half / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, bar, n0 + 64 * j, k0);
           } else {
-            tma_load_2d_pair(sb, tb_k, bar, k0, n0);
+            tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -202,13 +220,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint32_t idesc = make_idesc_f16(fmt, 2 * BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       for (int unit = pair_id; unit < num_units && ok; unit += num_pairs) {
-        const int width = unit >= sched.full_tiles ? BN / sched.split : BN;
-        const uint32_t idesc = make_idesc_f16(fmt, 2 * BM, width, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+        const WorkUnit wu = work_unit(unit, sched, k_blocks);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = wu.kb0; kb < wu.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             ok = false;
             break;
@@ -220,7 +238,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
             const uint64_t db = make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024);
-            umma_ss_pair(tmem_d, da, db, idesc, (kb | k) ? 1u : 0u);
+            umma_ss_pair(tmem_d, da, db, idesc, (kb > wu.kb0 || k) ? 1u : 0u);
           }
           umma_commit_pair(map_to_cta(empty_bar(stage), 0));
           umma_commit_pair(map_to_cta(empty_bar(stage), 1));
@@ -251,23 +269,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t leader_acc_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
-    const bool direct = push.n_peers > 0 || (dbg & 4);
+    const bool direct = push.n_peers > 0;
     constexpr int CHUNK_COLS = OUT_F32 ? 32 : 64;  // 128 bytes of output per row
     int chunk_counter = 0;
     for (int unit = pair_id; unit < num_units; unit += num_pairs) {
-      const WorkUnit wu = work_unit(unit, sched);
+      const WorkUnit wu = work_unit(unit, sched, k_blocks);
       const int row0 = wu.m * (2 * BM) + int(cta) * BM;
       const int row = row0 + quarter * 32 + lane;
+      const bool add_bias = BIAS && wu.part == 0;
       const int n0 = wu.n0;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       if (direct) {
 #pragma unroll 1
-        for (int c = 0; c < wu.width / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           const int col = n0 + c * 32;
           if (col >= N) break;
-          if (dbg & 1) continue;  // TEMP: skip the epilogue work
           uint32_t v[32];
           tmem_ld_32x32b_x32(taddr + c * 32, v);
           tmem_ld_wait();
@@ -277,7 +295,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int r_local = quarter * 32 + lane;          // row inside this CTA's 128-row slab
         const uint32_t swz = uint32_t(r_local & 7);
 #pragma unroll 1
-        for (int c = 0; c < wu.width / CHUNK_COLS; ++c) {
+        for (int c = 0; c < BN / CHUNK_COLS; ++c) {
           const int col = n0 + c * CHUNK_COLS;
           if (col >= N) break;
           const uint32_t buf = staging_base + uint32_t(chunk_counter & 1) * 16384u;
@@ -293,7 +311,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * alpha;
-            if (BIAS) {
+            if (add_bias) {
               if (OUT_F32) {
                 const float* b = reinterpret_cast<const float*>(bias_ptr) + col + h * 32;
 #pragma unroll
@@ -332,7 +350,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           fence_proxy_async_smem();
           named_barrier_sync(1, 128);
           if (ep_tid == 0) {
-            if (ACCUM) tma_reduce_add_2d(&tmap_d, buf, col, row0);
+            if (ACCUM || wu.partial) tma_reduce_add_2d(&tmap_d, buf, col, row0);
             else tma_store_2d(&tmap_d, buf, col, row0);
             tma_store_commit();
           }
@@ -382,8 +400,7 @@ const char* make_tmap_out(CUtensorMap* out, const void* ptr, int fmt, uint64_t r
                           uint32_t box_rows);
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
-static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, const CUtensorMap& td, const GemmArgs& g,
-                               int num_sms, cudaStream_t stream) {
+static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& g, int num_sms, cudaStream_t stream) {
   using namespace pair;
   auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
   static bool configured = false;
@@ -395,18 +412,31 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
-  int max_split = !g.split_tail ? 1 : (g.b_mn_major ? 2 : 4);
-  static const int dbg = getenv("ELF_B200_GEMM_DEBUG") ? atoi(getenv("ELF_B200_GEMM_DEBUG")) : 0;  // TEMP experiment switch
-  max_split |= dbg << 8;  // MN-major B is fetched in 64-wide boxes per CTA
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha,
-                                                       max_split, g.status, g.push);
+  // the direct (push) epilogue stores rows itself and cannot add partial sums
+  const int max_split = (!g.split_tail || g.push.n_peers > 0) ? 1 : 4;
+  const Schedule sched = make_schedule(g.M, g.N, (g.K + BK - 1) / BK, pairs, max_split);
+  if (sched.ksplit > 1 && !g.accumulate) {
+    // K-split tiles add their partial sums to D, so D must start at zero there.  The split
+    // tiles are the last ones of the tile order, all inside the row band that starts at the
+    // first row of the group holding the first of them: one memset clears that band (the
+    // whole tiles that share it are stored afterwards and simply overwrite the zeros).
+    int m, n;
+    tile_coords(sched.full_tiles, sched, &m, &n);
+    const long long row_start = (long long)(m / GROUP_M) * GROUP_M * 2 * BM;
+    const size_t esz = g.out_f32 ? 4 : 2;
+    char* base = static_cast<char*>(g.d) + size_t(row_start) * size_t(g.ldd) * esz;
+    const size_t rows = size_t(g.M - row_start);
+    cudaError_t e = g.ldd == g.N ? cudaMemsetAsync(base, 0, rows * size_t(g.N) * esz, stream)
+                                 : cudaMemset2DAsync(base, size_t(g.ldd) * esz, 0, size_t(g.N) * esz, rows, stream);
+    if (e != cudaSuccess) return e;
+  }
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, g.status, g.push);
   return cudaGetLastError();
 }
 
 template <bool A_MN, bool B_MN>
-static cudaError_t dispatch_pair(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4,
-                                 const CUtensorMap& td, int num_sms, cudaStream_t s) {
-#define ELFB_LAUNCH(F32, ACC, BI) return launch_pair<A_MN, B_MN, F32, ACC, BI>(ta, tb, tb2, tb4, td, g, num_sms, s)
+static cudaError_t dispatch_pair(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int num_sms, cudaStream_t s) {
+#define ELFB_LAUNCH(F32, ACC, BI) return launch_pair<A_MN, B_MN, F32, ACC, BI>(ta, tb, td, g, num_sms, s)
   if (g.out_f32) {
     if (g.accumulate) { if (g.bias) ELFB_LAUNCH(true, true, true); else ELFB_LAUNCH(true, true, false); }
     else              { if (g.bias) ELFB_LAUNCH(true, false, true); else ELFB_LAUNCH(true, false, false); }
@@ -420,25 +450,15 @@ static cudaError_t dispatch_pair(const GemmArgs& g, const CUtensorMap& ta, const
 const char* gemm_tcgen05_pair(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   using namespace pair;
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return nullptr;
-  CUtensorMap ta, tb, tb2, tb4;
+  CUtensorMap ta, tb;
   const char* err;
   if (g.a_mn_major) err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 64, BK);
   else              err = make_tmap_2d(&ta, g.a, g.fmt, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, BM);
   if (err) return err;
-  if (g.b_mn_major) {
-    err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, BK);
-    if (err) return err;
-    tb2 = tb;
-    tb4 = tb;
-  } else {
-    // per-CTA B boxes hold half of the unit's rows: 128, 64 or 32
-    err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 2);
-    if (err) return err;
-    err = make_tmap_2d(&tb2, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 4);
-    if (err) return err;
-    err = make_tmap_2d(&tb4, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 8);
-    if (err) return err;
-  }
+  // each CTA fetches half of the tile's B rows: one 128-row box (K-major) or two 64-wide boxes (MN-major)
+  if (g.b_mn_major) err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 64, BK);
+  else              err = make_tmap_2d(&tb, g.b, g.fmt, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 2);
+  if (err) return err;
   const int esz = g.out_f32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(g.d) & 15) != 0 || (g.ldd * esz) % 16 != 0) return "GEMM output must be 16-byte aligned with a 16-byte multiple row pitch";
   // output map for the TMA-store epilogue: 128-byte-wide, 128-row boxes
@@ -446,10 +466,10 @@ const char* gemm_tcgen05_pair(const GemmArgs& g, int num_sms, cudaStream_t strea
   err = make_tmap_out(&td, g.d, g.out_f32 ? 2 : g.fmt, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldd, g.out_f32 ? 32 : 64, BM);
   if (err) return err;
   cudaError_t e;
-  if (g.a_mn_major && g.b_mn_major) e = dispatch_pair<true, true>(g, ta, tb, tb2, tb4, td, num_sms, stream);
-  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_pair<false, true>(g, ta, tb, tb2, tb4, td, num_sms, stream);
-  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_pair<false, false>(g, ta, tb, tb2, tb4, td, num_sms, stream);
-  else e = dispatch_pair<true, false>(g, ta, tb, tb2, tb4, td, num_sms, stream);
+  if (g.a_mn_major && g.b_mn_major) e = dispatch_pair<true, true>(g, ta, tb, td, num_sms, stream);
+  else if (!g.a_mn_major && g.b_mn_major) e = dispatch_pair<false, true>(g, ta, tb, td, num_sms, stream);
+  else if (!g.a_mn_major && !g.b_mn_major) e = dispatch_pair<false, false>(g, ta, tb, td, num_sms, stream);
+  else e = dispatch_pair<true, false>(g, ta, tb, td, num_sms, stream);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 

@@ -1,0 +1,126 @@
+"""Causal grouped-query attention on the hand-written tcgen05 forward kernel.
+
+Forward: ``csrc/attention_sm100.cu`` (TMA -> shared memory -> ``tcgen05.mma`` with the score and
+output accumulators in tensor memory, online softmax by one thread per query row), which
+returns the output and the per-row log-sum-exp.  Backward: the library's fused attention
+backward fed with *our* output and log-sum-exp, so nothing is recomputed; when that entry
+point refuses the layout the gradient falls back to recomputation through SDPA.
+
+Parity: the reference takes attention from ``torch.nn.functional.scaled_dot_product_attention``
+inside the user's model (benchmarks/models/llama.py in the reference); this op is a drop-in for
+that call on packed projections.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext
+from . import gemm as _gemm
+
+__all__ = ["native_applicable_packed", "native_attention_packed", "native_applicable", "native_attention", "forward_packed"]
+
+HEAD_DIM = 128
+_MODE = os.environ.get("ELF_B200_ATTENTION", "library")  # "native" or "library"
+_BACKWARD = os.environ.get("ELF_B200_ATTENTION_BACKWARD", "library")  # "library" or "recompute"
+
+
+def set_mode(mode: str) -> None:
+    global _MODE
+    assert mode in ("native", "library")
+    _MODE = mode
+
+
+def native_applicable_packed(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, causal: bool) -> bool:
+    if _MODE != "native":
+        return False
+    return (
+        causal
+        and qkv.is_cuda
+        and qkv.dtype == torch.bfloat16
+        and qkv.dim() == 4
+        and qkv.shape[3] == HEAD_DIM
+        and qkv.shape[1] % 128 == 0
+        and qkv.shape[2] == n_heads + 2 * n_kv_heads
+        and n_heads % n_kv_heads == 0
+        and qkv.is_contiguous()
+    )
+
+
+def forward_packed(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, scale: float | None = None):
+    """Run the kernel: returns ``(out [B,S,Hq,D] bf16, lse [B,Hq,S] fp32)``."""
+    B, S = qkv.shape[0], qkv.shape[1]
+    out = torch.empty(B, S, n_heads, HEAD_DIM, device=qkv.device, dtype=qkv.dtype)
+    lse = torch.empty(B, n_heads, S, device=qkv.device, dtype=torch.float32)
+    _ext.get().attention_fwd(qkv, out, lse, n_heads, n_kv_heads, float(scale or 0.0), _gemm.status(qkv.device))
+    return out, lse
+
+
+_AUX: dict = {}
+
+
+def _library_backward(g, qkv, out, lse, hq, hkv, scale):
+    """Fused library backward (cuDNN) on our forward's output and log-sum-exp: nothing is
+    recomputed.  The gradients come back as three tensors and are packed by the caller."""
+    q = qkv[:, :, :hq].transpose(1, 2)
+    k = qkv[:, :, hq : hq + hkv].transpose(1, 2)
+    v = qkv[:, :, hq + hkv :].transpose(1, 2)
+    S = qkv.shape[1]
+    seed = _AUX.get(qkv.device)
+    if seed is None:
+        seed = _AUX[qkv.device] = torch.zeros((), device=qkv.device, dtype=torch.int64)  # dropout state: unused at p = 0
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+        g.transpose(1, 2), q, k, v, out.transpose(1, 2), lse.unsqueeze(-1), seed, seed, None, None, None, S, S, 0.0, True, scale=scale
+    )
+    return dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)
+
+
+def _recompute_backward(g, qkv, hq, hkv):
+    base = qkv.detach()
+    with torch.enable_grad():
+        q = base[:, :, :hq].requires_grad_()
+        k = base[:, :, hq : hq + hkv].requires_grad_()
+        v = base[:, :, hq + hkv :].requires_grad_()
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=hq != hkv).transpose(1, 2)
+    return torch.autograd.grad(o, (q, k, v), g)
+
+
+class _NativePacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, hq, hkv):
+        out, lse = forward_packed(qkv, hq, hkv)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.hq, ctx.hkv = hq, hkv
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        qkv, out, lse = ctx.saved_tensors
+        hq, hkv = ctx.hq, ctx.hkv
+        g = g.contiguous()
+        if _BACKWARD == "library":
+            dq, dk, dv = _library_backward(g, qkv, out, lse, hq, hkv, 1.0 / math.sqrt(HEAD_DIM))
+        else:
+            dq, dk, dv = _recompute_backward(g, qkv, hq, hkv)
+        dqkv = torch.empty_like(qkv)
+        dqkv[:, :, :hq].copy_(dq)
+        dqkv[:, :, hq : hq + hkv].copy_(dk)
+        dqkv[:, :, hq + hkv :].copy_(dv)
+        return dqkv, None, None
+
+
+def native_attention_packed(qkv: torch.Tensor, n_heads: int, n_kv_heads: int) -> torch.Tensor:
+    return _NativePacked.apply(qkv, n_heads, n_kv_heads)
+
+
+def native_applicable(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool) -> bool:
+    # separate q/k/v tensors would have to be packed first; the packed entry point is the fast path
+    return False
+
+
+def native_attention(q, k, v):  # pragma: no cover - guarded by native_applicable
+    raise NotImplementedError

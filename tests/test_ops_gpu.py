@@ -189,6 +189,50 @@ def test_fused_adamw(dev):
         assert rel_err(p, q) < 5e-3
 
 
+def _attention_reference(qkv, hq, hkv):
+    import math
+
+    q = qkv[:, :, :hq].transpose(1, 2)
+    k = qkv[:, :, hq : hq + hkv].transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+    v = qkv[:, :, hq + hkv :].transpose(1, 2).repeat_interleave(hq // hkv, dim=1)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(q.shape[-1])
+    n = s.shape[-1]
+    s = s.masked_fill(torch.triu(torch.ones(n, n, device=s.device, dtype=torch.bool), 1), float("-inf"))
+    return (torch.softmax(s, -1) @ v).transpose(1, 2), torch.logsumexp(s, -1)
+
+
+@pytest.mark.parametrize("batch,seq,hq,hkv,mult", [(1, 128, 1, 1, 1.0), (2, 384, 4, 2, 1.0), (1, 1024, 8, 2, 3.0)])
+def test_attention_forward_kernel(dev, batch, seq, hq, hkv, mult):
+    """tcgen05 flash attention forward against fp32 softmax(QK^T)V; `mult` widens the score
+    range so that the lazy re-scaling of the running maximum is exercised."""
+    from elf_b200.ops import attention_native as A
+    from elf_b200.ops import gemm as G
+
+    torch.manual_seed(seq + hq)
+    qkv = (torch.randn(batch, seq, hq + 2 * hkv, 128, device=dev) * mult).bfloat16()
+    out, lse = A.forward_packed(qkv, hq, hkv)
+    G.check_status(dev)
+    ref_out, ref_lse = _attention_reference(qkv.float(), hq, hkv)
+    assert rel_err(out, ref_out) < 1e-2
+    assert (lse - ref_lse).abs().max().item() < 2e-2
+
+
+def test_attention_native_backward(dev):
+    """Gradient of the native attention op (own forward + fused backward on its results)
+    against fp32 autograd of the plain formula."""
+    from elf_b200.ops import attention_native as A
+
+    torch.manual_seed(7)
+    hq, hkv = 4, 2
+    qkv = torch.randn(2, 256, hq + 2 * hkv, 128, device=dev).bfloat16()
+    g = torch.randn(2, 256, hq, 128, device=dev).bfloat16()
+    x = qkv.clone().requires_grad_()
+    A.native_attention_packed(x, hq, hkv).backward(g)
+    x32 = qkv.float().requires_grad_()
+    _attention_reference(x32, hq, hkv)[0].backward(g.float())
+    assert rel_err(x.grad, x32.grad) < 2e-2
+
+
 def test_llama_layer_matches_fp32_reference(dev):
     """A decoder layer on the kernels vs. the same module in fp32 on torch ops."""
     from elf_b200.models.llama import LlamaConfig, LlamaDecoderLayer, init_llama_
