@@ -7,15 +7,18 @@
 //     P_j = exp2(S_j*c - m)    softmax warps: one thread per query row, S read with tcgen05.ld,
 //                              P written to its own TMEM columns as packed bf16 with tcgen05.st
 //     O  += P_j V_j            tcgen05.mma with A = P_j straight from TMEM, B = V_j (MN-major)
-// Roles (224 threads): warp 0 = TMA producer for Q and K, warp 6 = TMA producer for V (two
+// Roles (384 threads): warp 0 = TMA producer for Q and K, warp 2 = TMA producer for V (two
 // independent rings of 3 stages, so a late V slot never delays a K load), warp 1 = MMA issuer
-// (one thread), warps 2..5 = softmax / correction / epilogue.  S and P are double-buffered in
+// (one thread), warps 4..11 = softmax / correction / epilogue: two threads per query row, each
+// owning 64 of the tile's 128 key columns (a single warp per scheduler cannot hide the
+// latencies of its own dependent instructions; two can), exchanging their partial row maxima
+// through shared memory.  S and P are double-buffered in
 // TMEM so that Q K_{j+1}^T runs while softmax works on tile j and P_j V_j runs while softmax
 // works on tile j+1; all rings and buffers keep rotating across item boundaries, so the next
 // item's first loads and its first MMA overlap the current item's epilogue.  The running
 // maximum is only raised (and O rescaled through TMEM) when a row's maximum grows by more
 // than 2^8, which keeps exp2 in range and makes rescaling rare after the first tiles.  The
-// output leaves straight from registers (each thread owns a 256-byte row of O).  Every
+// output leaves straight from registers (each thread owns 128 bytes of a row of O).  Every
 // mbarrier wait is bounded.
 //
 // TMEM columns: [0,128) S0, [128,256) S1, [256,384) O, [384,448) P0, [448,512) P1 (bf16 pairs).
@@ -39,12 +42,13 @@ constexpr int BKV = 128;          // keys per tile
 constexpr int TILE_BYTES = 128 * D * 2;  // 32 KiB: two 64-column boxes of 128 rows
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 3;
-constexpr int NUM_THREADS = 224;
+constexpr int NUM_THREADS = 384;
+constexpr int XCHG_BYTES = 2 * 2 * 128 * 4;  // [parity][column half][row] partial row maxima / sums
 constexpr int TMEM_COLS = 512;
 __host__ __device__ constexpr int s_col(int s) { return s * 128; }
 __host__ __device__ constexpr int p_col(int s) { return 384 + s * 64; }
 constexpr int O_COL = 256;
-constexpr size_t SMEM_BYTES = size_t(TILE_BYTES) * (1 + 2 * KV_STAGES) + 1024 + 256;
+constexpr size_t SMEM_BYTES = size_t(TILE_BYTES) * (1 + 2 * KV_STAGES) + XCHG_BYTES + 256;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -76,13 +80,18 @@ struct ItemWalk {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int batch, int seq, int n_heads,
                      int n_kv_heads, float scale_log2, int* __restrict__ status) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  if ((smem_base & 1023u) != 0) {  // the 128-byte swizzle needs 1024-byte aligned tiles
+    if (threadIdx.x == 0 && status != nullptr && atomicCAS(status, kOk, kErrBadShape) == kOk) status[1] = 2900000;
+    return;
+  }
+  uint8_t* smem_aligned = smem_raw;
   const uint32_t q_smem = smem_base;
   auto k_smem = [&](int s) { return smem_base + TILE_BYTES * (1 + s); };
   auto v_smem = [&](int s) { return smem_base + TILE_BYTES * (1 + KV_STAGES + s); };
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + size_t(TILE_BYTES) * (1 + 2 * KV_STAGES));
+  float* xchg = reinterpret_cast<float*>(smem_aligned + size_t(TILE_BYTES) * (1 + 2 * KV_STAGES));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_aligned + size_t(TILE_BYTES) * (1 + 2 * KV_STAGES) + XCHG_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   enum {
     Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + KV_STAGES, V_FULL = K_EMPTY + KV_STAGES, V_EMPTY = V_FULL + KV_STAGES,
@@ -91,6 +100,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
   auto bar = [&](int slot) { return bar0 + 8u * slot; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* pair_seq = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [8]: exchanges published by each softmax warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -105,6 +115,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    for (int w = 0; w < 8; ++w) pair_seq[w] = 0;
     mbar_init(bar(Q_FULL), 1);
     mbar_init(bar(Q_EMPTY), 1);
     for (int s = 0; s < KV_STAGES; ++s) {
@@ -115,7 +126,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(P_FULL + s), 4);  // one arrival per softmax warp
+      mbar_init(bar(P_FULL + s), 8);  // one arrival per softmax warp
       mbar_init(bar(PV_DONE + s), 1);
     }
     mbar_init(bar(O_FINAL), 1);
@@ -158,7 +169,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
     }
     __syncwarp();
-  } else if (warp == 6) {
+  } else if (warp == 2) {
     // ------------------------------------------------------------------ TMA producer: V
     if (lane == 0) {
       int stage = 0;
@@ -234,45 +245,79 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax / correction / epilogue
     const int quarter = warp & 3;                 // TMEM lanes [32*quarter, +32)
+    const int half = (warp - 4) >> 2;             // key columns [64*half, +64) of every tile
     const int r = quarter * 32 + lane;            // query row inside the tile
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    const int my_slot = warp - 4, partner_slot = (warp - 4) ^ 4;  // the two warps that share these rows
     int g = 0;
+    int xc = 0;  // exchanges so far
     bool ok = true;
+    // Both threads of a row publish a value and read the partner's.  Values are double-buffered by
+    // the parity of the exchange count; a warp announces its n-th values by writing n to its
+    // sequence word and waits (bounded) for the partner warp's.  A warp can only overwrite a buffer
+    // two exchanges later, which it reaches after the partner has announced the exchange in
+    // between, that is after the partner has finished reading this one.
+    auto exchange = [&](float mine, float* theirs) -> bool {
+      float* buf = xchg + (xc & 1) * 256;
+      buf[half * 128 + r] = mine;
+      ++xc;
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) pair_seq[my_slot] = xc;
+      if (pair_seq[partner_slot] < xc) {
+        const unsigned long long t0 = globaltimer_ns();
+        for (uint32_t spin = 1; pair_seq[partner_slot] < xc; ++spin) {
+          if ((spin & 0xffu) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+              *abort_flag = 1;
+              return false;
+            }
+          }
+        }
+      }
+      __threadfence_block();
+      *theirs = buf[(half ^ 1) * 128 + r];
+      return true;
+    };
     Item it;
     for (int round = 0; ok && walk.get(round, &it); ++round) {
       const int n_kv = it.q_tile + 1;
       float m_ref = -INFINITY;  // reference maximum (scaled, log2 domain) the stored exponentials refer to
-      float l = 0.f;            // running sum of exp2(x * c - m_ref)
+      float l = 0.f;            // this thread's share of the running sum of exp2(x * c - m_ref)
       for (int j = 0; j < n_kv; ++j) {
         const int t = g + j;
         const int s = t & 1;
         if (!mbar_wait(bar(S_FULL + s), uint32_t(t >> 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        // the whole score row (raw, unscaled) in one go: four loads in flight, one wait
-        uint32_t v[4][32];
+        // this thread's 64 raw scores: two loads in flight, one wait
+        uint32_t v[2][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tmem_base + lane_off + s_col(s) + c * 32, v[c]);
+        for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(tmem_base + lane_off + s_col(s) + half * 64 + c * 32, v[c]);
         tmem_ld_wait();
         if (j == it.q_tile) {  // diagonal tile: keys after the query are masked
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (c * 32 + i > r) v[c][i] = 0xff800000u;  // -inf
+              if (half * 64 + c * 32 + i > r) v[c][i] = 0xff800000u;  // -inf
         }
-        // row maximum over eight independent chains
-        float mx8[8];
+        float mx4[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) mx8[q] = __uint_as_float(v[q >> 1][(q & 1) * 16]);
+        for (int q = 0; q < 4; ++q) mx4[q] = __uint_as_float(v[q >> 1][(q & 1) * 16]);
 #pragma unroll
         for (int i = 1; i < 16; ++i)
 #pragma unroll
-          for (int q = 0; q < 8; ++q) mx8[q] = fmaxf(mx8[q], __uint_as_float(v[q >> 1][(q & 1) * 16 + i]));
-        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * scale_log2;
-        // raise the reference maximum only when it pays (always on the first tile)
+          for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], __uint_as_float(v[q >> 1][(q & 1) * 16 + i]));
+        const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float theirs;
+        if (!exchange(mine, &theirs)) { ok = false; break; }
+        const float mx = fmaxf(mine, theirs) * scale_log2;
+        // raise the reference maximum only when it pays (always on the first tile); both
+        // threads of a row see the same numbers and take the same decision
         const bool raise = mx > m_ref + RESCALE_THRESHOLD;
         if (__any_sync(0xffffffffu, raise)) {
           const float m_new = raise ? mx : m_ref;
@@ -283,9 +328,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
             // O holds the sum up to tile j-1 once P_{j-1} V_{j-1} has completed
             if (!mbar_wait(bar(PV_DONE + ((t - 1) & 1)), uint32_t((t - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t o_addr = tmem_base + lane_off + O_COL;
+            const uint32_t o_addr = tmem_base + lane_off + O_COL + half * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {  // rare after the first tiles: kept rolled to save registers
+            for (int c = 0; c < 2; ++c) {  // rare after the first tiles: kept rolled to save registers
               uint32_t o[32];
               tmem_ld_32x32b_x32(o_addr + c * 32, o);
               tmem_ld_wait();
@@ -300,19 +345,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
         if (t >= 2 && !mbar_wait(bar(PV_DONE + s), uint32_t((t - 2) >> 1) & 1u, abort_flag)) { ok = false; break; }
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {  // 64 keys -> 32 packed columns per store
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int e = c * 64 + 2 * i;
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[e >> 5][e & 31]), scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[(e + 1) >> 5][(e + 1) & 31]), scale_log2, neg_m));
-            sum4[i & 3] += p0 + p1;
-            pk[i] = pack_bf16x2(p0, p1);
-          }
-          tmem_st_32x32b_x32(tmem_base + lane_off + p_col(s) + c * 32, pk);
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[i >> 4][(2 * i) & 31]), scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[i >> 4][(2 * i + 1) & 31]), scale_log2, neg_m));
+          sum4[i & 3] += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
         }
+        tmem_st_32x32b_x32(tmem_base + lane_off + p_col(s) + half * 32, pk);
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tmem_st_wait();
         tc_fence_before_sync();
@@ -321,21 +362,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
       }
       if (!ok) break;
       g += n_kv;
-      // ---- epilogue: O / l -> bf16, straight from registers (each thread owns one 256-byte row)
+      // ---- epilogue: O / l -> bf16, straight from registers (each thread owns 128 bytes of a row)
+      float l_other;
+      if (!exchange(l, &l_other)) break;
+      const float l_row = l + l_other;
       if (!mbar_wait(bar(O_FINAL), uint32_t(round) & 1u, abort_flag)) break;
       tc_fence_after_sync();
-      const float inv_l = 1.f / l;
+      const float inv_l = 1.f / l_row;
       const size_t token = size_t(it.b) * seq + size_t(it.q_tile) * BQ + r;
-      uint4* dst = reinterpret_cast<uint4*>(out + (token * n_heads + it.head) * D);
-      const uint32_t o_addr = tmem_base + lane_off + O_COL;
-      uint32_t o[4][32];
+      uint4* dst = reinterpret_cast<uint4*>(out + (token * n_heads + it.head) * D + half * 64);
+      const uint32_t o_addr = tmem_base + lane_off + O_COL + half * 64;
+      uint32_t o[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(o_addr + c * 32, o[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(o_addr + c * 32, o[c]);
       tmem_ld_wait();
       // O may be overwritten by the next item's first P V from here on: that product waits for this
       // warp's next arrival on P_FULL, which program order puts after these loads
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 w;
@@ -345,7 +389,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16
           w.w = pack_bf16x2(__uint_as_float(o[c][8 * q + 6]) * inv_l, __uint_as_float(o[c][8 * q + 7]) * inv_l);
           dst[c * 4 + q] = w;
         }
-      lse[(size_t(it.b) * n_heads + it.head) * seq + it.q_tile * BQ + r] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      if (half == 0) lse[(size_t(it.b) * n_heads + it.head) * seq + it.q_tile * BQ + r] = (m_ref + log2f(l_row)) * 0.6931471805599453f;
     }
   }
 
