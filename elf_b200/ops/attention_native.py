@@ -2,9 +2,10 @@
 
 Forward: ``csrc/attention_sm100.cu`` (TMA -> shared memory -> ``tcgen05.mma`` with the score and
 output accumulators in tensor memory, online softmax by one thread per query row), which
-returns the output and the per-row log-sum-exp.  Backward: the library's fused attention
-backward fed with *our* output and log-sum-exp, so nothing is recomputed; when that entry
-point refuses the layout the gradient falls back to recomputation through SDPA.
+returns the output and the per-row log-sum-exp.  Backward: ``csrc/attention_bwd_sm100.cu``
+(dK / dV accumulated in tensor memory per key tile, dQ summed across key tiles in an fp32
+buffer).  ``ELF_B200_ATTENTION_BACKWARD=library`` feeds the library's fused backward with
+*our* output and log-sum-exp instead; ``recompute`` re-runs SDPA under autograd.
 
 Parity: the reference takes attention from ``torch.nn.functional.scaled_dot_product_attention``
 inside the user's model (benchmarks/models/llama.py in the reference); this op is a drop-in for
@@ -22,11 +23,11 @@ import torch.nn.functional as F
 from . import _ext
 from . import gemm as _gemm
 
-__all__ = ["native_applicable_packed", "native_attention_packed", "native_applicable", "native_attention", "forward_packed"]
+__all__ = ["native_applicable_packed", "native_attention_packed", "native_applicable", "native_attention", "forward_packed", "backward_packed"]
 
 HEAD_DIM = 128
 _MODE = os.environ.get("ELF_B200_ATTENTION", "library")  # "native" or "library"
-_BACKWARD = os.environ.get("ELF_B200_ATTENTION_BACKWARD", "library")  # "library" or "recompute"
+_BACKWARD = os.environ.get("ELF_B200_ATTENTION_BACKWARD", "native")  # "native", "library" or "recompute"
 
 
 def set_mode(mode: str) -> None:
@@ -79,6 +80,29 @@ def _library_backward(g, qkv, out, lse, hq, hkv, scale):
     return dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)
 
 
+_SCRATCH: dict = {}
+
+
+def backward_packed(g: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, hq: int, hkv: int, scale: float | None = None) -> torch.Tensor:
+    """Own backward kernels (``csrc/attention_bwd_sm100.cu``): returns the packed ``dqkv``.
+
+    The fp32 dQ accumulator and the two per-row statistics are cached per device and shape; the
+    kernels leave the accumulator zeroed, so consecutive calls on one stream can share it."""
+    B, S = qkv.shape[0], qkv.shape[1]
+    key = (qkv.device, B, S, hq)
+    scratch = _SCRATCH.get(key)
+    if scratch is None:
+        scratch = _SCRATCH[key] = (
+            torch.zeros(B, S, hq, HEAD_DIM, device=qkv.device, dtype=torch.float32),
+            torch.empty(B, hq, S, device=qkv.device, dtype=torch.float32),
+            torch.empty(B, hq, S, device=qkv.device, dtype=torch.float32),
+        )
+    dq_acc, lse2, delta = scratch
+    dqkv = torch.empty_like(qkv)
+    _ext.get().attention_bwd(qkv, out, g.contiguous(), lse, dqkv, dq_acc, lse2, delta, hq, hkv, float(scale or 0.0), _gemm.status(qkv.device))
+    return dqkv
+
+
 def _recompute_backward(g, qkv, hq, hkv):
     base = qkv.detach()
     with torch.enable_grad():
@@ -102,6 +126,8 @@ class _NativePacked(torch.autograd.Function):
         qkv, out, lse = ctx.saved_tensors
         hq, hkv = ctx.hq, ctx.hkv
         g = g.contiguous()
+        if _BACKWARD == "native":
+            return backward_packed(g, qkv, out, lse, hq, hkv), None, None
         if _BACKWARD == "library":
             dq, dk, dv = _library_backward(g, qkv, out, lse, hq, hkv, 1.0 / math.sqrt(HEAD_DIM))
         else:
