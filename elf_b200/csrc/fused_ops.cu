@@ -60,10 +60,12 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------------ RMSNorm
-constexpr int RMS_THREADS = 256;
-constexpr int RMS_MAX_VEC = 4;  // rows up to 256*4*8 = 8192 elements stay in registers
+// One block per row, the row held in registers.  Rows of up to 4096 elements run on 128-thread
+// blocks (four 16-byte vectors per thread): twice as many resident blocks per SM as with 256
+// threads, so twice as many bytes in flight per SM, and half as many warps in the block-wide sum.
+constexpr int RMS_MAX_VEC = 4;  // rows up to RMS_THREADS*4*8 elements stay in registers (4096 / 8192)
 
-template <bool RESIDUAL>
+template <bool RESIDUAL, int RMS_THREADS>
 __global__ void __launch_bounds__(RMS_THREADS) rmsnorm_fwd_kernel(const Bf16x8* __restrict__ x, const Bf16x8* __restrict__ res,
                                                                   const Bf16x8* __restrict__ w, Bf16x8* __restrict__ y,
                                                                   Bf16x8* __restrict__ h, float* __restrict__ rstd, int dim8,
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(RMS_THREADS) rmsnorm_fwd_kernel(const Bf16x8* 
 //        the 8 lanes are summed through shared memory and written as one partial row.
 constexpr int RMS_DW_SPLITS = 64;
 
-template <bool DRES>
+template <bool DRES, int RMS_THREADS>
 __global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_dx_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
                                                                      const Bf16x8* __restrict__ w, const float* __restrict__ rstd,
                                                                      const Bf16x8* __restrict__ dres, Bf16x8* __restrict__ dx,
@@ -462,12 +464,20 @@ cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, 
   if (rows == 0) return cudaSuccess;
   if (dim % 8) return cudaErrorInvalidValue;
   const int dim8 = dim / 8;
-  if (residual)
-    rmsnorm_fwd_kernel<true><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)x, (const Bf16x8*)residual, (const Bf16x8*)w,
-                                                          (Bf16x8*)y, (Bf16x8*)h, rstd, dim8, 1.f / dim, eps);
-  else
-    rmsnorm_fwd_kernel<false><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)x, nullptr, (const Bf16x8*)w, (Bf16x8*)y, nullptr,
-                                                           rstd, dim8, 1.f / dim, eps);
+  const bool narrow = dim8 <= 128 * RMS_MAX_VEC;
+  if (residual) {
+    if (narrow)
+      rmsnorm_fwd_kernel<true, 128><<<rows, 128, 0, s>>>((const Bf16x8*)x, (const Bf16x8*)residual, (const Bf16x8*)w, (Bf16x8*)y, (Bf16x8*)h, rstd, dim8,
+                                                         1.f / dim, eps);
+    else
+      rmsnorm_fwd_kernel<true, 256><<<rows, 256, 0, s>>>((const Bf16x8*)x, (const Bf16x8*)residual, (const Bf16x8*)w, (Bf16x8*)y, (Bf16x8*)h, rstd, dim8,
+                                                         1.f / dim, eps);
+  } else {
+    if (narrow)
+      rmsnorm_fwd_kernel<false, 128><<<rows, 128, 0, s>>>((const Bf16x8*)x, nullptr, (const Bf16x8*)w, (Bf16x8*)y, nullptr, rstd, dim8, 1.f / dim, eps);
+    else
+      rmsnorm_fwd_kernel<false, 256><<<rows, 256, 0, s>>>((const Bf16x8*)x, nullptr, (const Bf16x8*)w, (Bf16x8*)y, nullptr, rstd, dim8, 1.f / dim, eps);
+  }
   return cudaGetLastError();
 }
 
@@ -476,14 +486,22 @@ int rmsnorm_backward_blocks(int rows) { return RMS_DW_SPLITS; }
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
                              float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  if (dim % 8 || dim > RMS_THREADS * RMS_MAX_VEC * 8) return cudaErrorInvalidValue;
+  if (dim % 8 || dim > 256 * RMS_MAX_VEC * 8) return cudaErrorInvalidValue;
   const int dim8 = dim / 8;
-  if (dres_in)
-    rmsnorm_bwd_dx_kernel<true><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd,
-                                                             (const Bf16x8*)dres_in, (Bf16x8*)dx, dim8, 1.f / dim);
-  else
-    rmsnorm_bwd_dx_kernel<false><<<rows, RMS_THREADS, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr,
-                                                              (Bf16x8*)dx, dim8, 1.f / dim);
+  const bool narrow = dim8 <= 128 * RMS_MAX_VEC;
+  if (dres_in) {
+    if (narrow)
+      rmsnorm_bwd_dx_kernel<true, 128><<<rows, 128, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, (const Bf16x8*)dres_in, (Bf16x8*)dx,
+                                                            dim8, 1.f / dim);
+    else
+      rmsnorm_bwd_dx_kernel<true, 256><<<rows, 256, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, (const Bf16x8*)dres_in, (Bf16x8*)dx,
+                                                            dim8, 1.f / dim);
+  } else {
+    if (narrow)
+      rmsnorm_bwd_dx_kernel<false, 128><<<rows, 128, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr, (Bf16x8*)dx, dim8, 1.f / dim);
+    else
+      rmsnorm_bwd_dx_kernel<false, 256><<<rows, 256, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, (const Bf16x8*)w, rstd, nullptr, (Bf16x8*)dx, dim8, 1.f / dim);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const dim3 grid((dim8 + 31) / 32, RMS_DW_SPLITS);

@@ -44,6 +44,12 @@ constexpr int GROUP_M = 4;  // in units of 256-row pair tiles
 constexpr int STAGING_BYTES = 2 * 16384;  // two 128-row x 128-byte chunks for the TMA-store epilogue
 constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
 
+// Tensor maps over the peers' copies of D (same shape and pitch as the local D), used when the
+// epilogue also pushes its tiles to other GPUs.
+struct alignas(64) PeerMaps {
+  CUtensorMap m[kMaxPeers];
+};
+
 struct WorkUnit {
   int m, n0;      // tile row (in 256-row units) and first output column
   int kb0, kb1;   // range of 64-wide k-blocks this unit contracts over
@@ -120,7 +126,8 @@ template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_d, void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
-                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push) {
+                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push,
+                         const __grid_constant__ PeerMaps peer_maps) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -259,17 +266,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
-    // Two paths.  With a push target (once per step and matrix) every thread stores its row
-    // straight to local and peer memory.  Otherwise the tile leaves through shared memory:
-    // each thread converts its row of a 128-byte-wide column chunk into a swizzled staging
-    // buffer and one thread hands the chunk to TMA (store, or add-reduce in L2 when
-    // accumulating), so the LSU issues no global stores and D is written in full lines.
+    // The tile leaves through shared memory: each thread converts its row of a 128-byte-wide
+    // column chunk into a swizzled staging buffer and one thread hands the chunk to TMA (store,
+    // or add-reduce in L2 when accumulating), so the LSU issues no global stores and D is
+    // written in full lines.  With a push target (once per step and matrix) the same staged
+    // chunk is also TMA-stored into every peer's copy of D over NVLink; when that launch
+    // accumulates, the threads read the old values of their rows themselves and the finished
+    // sum is stored (locally and remotely) instead of being add-reduced.
     const int quarter = warp & 3;
     const int ep_tid = threadIdx.x - 64;  // 0..127 over the four epilogue warps
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t leader_acc_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
-    const bool direct = push.n_peers > 0;
+    const bool pushing = push.n_peers > 0;
     constexpr int CHUNK_COLS = OUT_F32 ? 32 : 64;  // 128 bytes of output per row
     int chunk_counter = 0;
     for (int unit = pair_id; unit < num_units; unit += num_pairs) {
@@ -281,17 +290,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      if (direct) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= N) break;
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, v);
-          tmem_ld_wait();
-          store_accumulator_chunk<OUT_F32, ACCUM, BIAS>(v, row, col, M, N, d_ptr, ldd, bias_ptr, fmt, alpha, push);
-        }
-      } else {
+      {
         const int r_local = quarter * 32 + lane;          // row inside this CTA's 128-row slab
         const uint32_t swz = uint32_t(r_local & 7);
 #pragma unroll 1
@@ -325,6 +324,42 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
               }
             }
+            if (ACCUM && pushing && row < M) {  // the sum itself is stored: fetch what D holds
+              const int c0 = col + h * 32;
+              if (OUT_F32) {
+                const float* old = reinterpret_cast<const float*>(d_ptr) + (long long)row * ldd + c0;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  if (c0 + 4 * q + 4 <= N) {
+                    const float4 o4 = *reinterpret_cast<const float4*>(old + 4 * q);
+                    f[4 * q] += o4.x; f[4 * q + 1] += o4.y; f[4 * q + 2] += o4.z; f[4 * q + 3] += o4.w;
+                  } else {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                      if (c0 + 4 * q + t < N) f[4 * q + t] += old[4 * q + t];
+                  }
+                }
+              } else {
+                const uint16_t* old = reinterpret_cast<const uint16_t*>(d_ptr) + (long long)row * ldd + c0;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  if (c0 + 8 * q + 8 <= N) {
+                    const uint4 o4 = *reinterpret_cast<const uint4*>(old + 8 * q);
+                    const uint32_t w[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                      const uint16_t lo = uint16_t(w[t] & 0xffffu), hi = uint16_t(w[t] >> 16);
+                      f[8 * q + 2 * t] += fmt == 1u ? __bfloat162float(__ushort_as_bfloat16(lo)) : __half2float(__ushort_as_half(lo));
+                      f[8 * q + 2 * t + 1] += fmt == 1u ? __bfloat162float(__ushort_as_bfloat16(hi)) : __half2float(__ushort_as_half(hi));
+                    }
+                  } else {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t)
+                      if (c0 + 8 * q + t < N) f[8 * q + t] += fmt == 1u ? __bfloat162float(__ushort_as_bfloat16(old[8 * q + t])) : __half2float(__ushort_as_half(old[8 * q + t]));
+                  }
+                }
+              }
+            }
             if (OUT_F32) {
 #pragma unroll
               for (int q = 0; q < 8; ++q) {  // eight 16-byte vectors = the whole 128-byte row
@@ -350,8 +385,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           fence_proxy_async_smem();
           named_barrier_sync(1, 128);
           if (ep_tid == 0) {
-            if (ACCUM || wu.partial) tma_reduce_add_2d(&tmap_d, buf, col, row0);
+            if ((ACCUM && !pushing) || wu.partial) tma_reduce_add_2d(&tmap_d, buf, col, row0);
             else tma_store_2d(&tmap_d, buf, col, row0);
+            for (int p = 0; p < push.n_peers; ++p) tma_store_2d(&peer_maps.m[p], buf, col, row0);
             tma_store_commit();
           }
           ++chunk_counter;
@@ -365,7 +401,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         acc_phase ^= 1u;
       }
     }
-    if (!direct && ep_tid == 0) tma_store_wait_all();  // every store of this CTA has landed
+    if (ep_tid == 0) tma_store_wait_all();  // every store of this CTA has been performed, the remote ones included
   }
 
   // ------------------------------------------------------------------ common exit
@@ -412,7 +448,7 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
-  // the direct (push) epilogue stores rows itself and cannot add partial sums
+  // a pushing launch stores finished sums; partial sums of a K-split tile cannot be pushed
   const int max_split = (!g.split_tail || g.push.n_peers > 0) ? 1 : 4;
   const Schedule sched = make_schedule(g.M, g.N, (g.K + BK - 1) / BK, pairs, max_split);
   if (sched.ksplit > 1 && !g.accumulate) {
@@ -430,7 +466,13 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
                                  : cudaMemset2DAsync(base, size_t(g.ldd) * esz, 0, size_t(g.N) * esz, rows, stream);
     if (e != cudaSuccess) return e;
   }
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, g.status, g.push);
+  PeerMaps peers;
+  for (int p = 0; p < kMaxPeers; ++p) peers.m[p] = td;  // unused entries stay valid maps
+  for (int p = 0; p < g.push.n_peers; ++p) {
+    if (make_tmap_out(&peers.m[p], g.push.peer_out[p], g.out_f32 ? 2 : g.fmt, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldd, g.out_f32 ? 32 : 64, BM) != nullptr)
+      return cudaErrorInvalidValue;
+  }
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, g.status, g.push, peers);
   return cudaGetLastError();
 }
 
