@@ -43,6 +43,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only; the result is then not the headline number)")
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
     return ap.parse_args()
 
 
@@ -52,7 +53,7 @@ def run_ours(args):
 
     from benchmarks.benchmark_utils import ClockSampler, init_dist, max_over_ranks
     from elf_b200 import Pipeline, Placement
-    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, head_cost_in_layers, layers_per_stage, llama_loss_fn
+    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, half_layer_ranges, head_cost_in_layers, llama_loss_fn, llama_stage_costs
     from elf_b200.ops import _ext
     from elf_b200.optim import DummyOptimizer, FusedAdamW
     from dataclasses import replace
@@ -70,21 +71,27 @@ def run_ours(args):
     placement = Placement.default(args.scheduler, pp)
     pp_rank = rank % pp
     mine = placement.get_ids(pp_rank)
-    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement))
+    # stage boundaries may fall between the attention half and the MLP half of a layer: whole
+    # layers cannot balance 32 layers + the LM head (2.2 layers' worth) over 8 ranks
+    split_layers = pp > 1 and not args.whole_layers
+    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement), split_layers=split_layers)
     parts = [stages[i] for i in mine]
-    counts = layers_per_stage(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg))
+    stage_costs = llama_stage_costs(cfg, len(placement), list(placement), split_layers)
+    if split_layers:
+        counts = [(b - a) / 2 for a, b in half_layer_ranges(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg))[0]]
+    else:
+        counts = [round(c - (head_cost_in_layers(cfg) if i == len(placement) - 1 else 0.0)) for i, c in enumerate(stage_costs)]
     scheduler, sched_note = args.scheduler, args.scheduler
     if args.scheduler == "zbv" and pp > 1:
         # ZB-V laid out for what the stages cost: layer counts differ per stage, the last stage
-        # also runs the LM head, and B is longer than F and W (attention backward).  Up to 3p
+        # also runs the LM head, and B is longer than F and W (attention backward).  Up to 6p
         # live (stage, micro-batch) activations per rank instead of 2p: memory is not scarce here.
         import functools
 
         from elf_b200.scheduling.schedulers import generate_zbv_schedule
 
-        stage_costs = [c + (head_cost_in_layers(cfg) if i == len(placement) - 1 else 0.0) for i, c in enumerate(counts)]
-        scheduler = functools.partial(generate_zbv_schedule, cap=3 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
-        sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, at most 3p live activations per rank)"
+        scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
+        sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
     pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none")
     params = list(pipe.parameters())
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()

@@ -134,6 +134,50 @@ class LlamaDecoderLayer(nn.Module):
         return x + self.w_down(_f.swiglu(self.w_gate_up(h2)))
 
 
+class LlamaAttentionBlock(nn.Module):
+    """First half of a decoder layer (norm, QKV projection, RoPE, attention, output projection,
+    residual add) as a module of its own, for stage boundaries that cut a layer in two."""
+
+    _elf_leaf = True
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        d, hd = cfg.d_model, cfg.head_dim
+        self.n_heads, self.n_kv_heads, self.head_dim, self.seq_len = cfg.n_heads, cfg.n_kv_heads, hd, cfg.seq_len
+        self.theta = cfg.rope_theta
+        self.norm1 = RMSNorm(d, cfg.eps)
+        self.wqkv = nn.Linear(d, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, bias=False)
+        self.wo = nn.Linear(cfg.n_heads * hd, d, bias=False)
+        self._rope = None
+
+    _tables = LlamaDecoderLayer._tables
+
+    def forward(self, x):
+        b, s, d = x.shape
+        hq, hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        cos, sin = self._tables(x.device, s)
+        qkv = self.wqkv(self.norm1(x).view(b * s, d))
+        qkv = _f.rope_(qkv, cos, sin, hq + hkv, hd, s).view(b, s, hq + 2 * hkv, hd)
+        a = _attn.attention_packed(qkv, hq, hkv, causal=True).reshape(b, s, hq * hd)
+        return x + self.wo(a)
+
+
+class LlamaMLPBlock(nn.Module):
+    """Second half of a decoder layer (norm, gate/up projection, SwiGLU, down projection, residual add)."""
+
+    _elf_leaf = True
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        d = cfg.d_model
+        self.norm2 = RMSNorm(d, cfg.eps)
+        self.w_gate_up = nn.Linear(d, 2 * cfg.ffn, bias=False)
+        self.w_down = nn.Linear(cfg.ffn, d, bias=False)
+
+    def forward(self, x):
+        return x + self.w_down(_f.swiglu(self.w_gate_up(self.norm2(x))))
+
+
 class LlamaHead(nn.Module):
     _elf_leaf = True
 
@@ -210,16 +254,188 @@ def layers_per_stage(n_layers: int, n_stages: int, placement: Optional[Sequence[
     return counts
 
 
-def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None) -> List[Optional[LlamaStage]]:
+ATTENTION_SHARE = 0.3  # measured share of a decoder layer's forward+backward time spent in its attention half
+
+
+def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0, attention_share: float = ATTENTION_SHARE):
+    """Split the 2·n_layers half-layers (attention half, MLP half, attention half, ...) into
+    ``n_stages`` contiguous ranges so that the busiest *rank* has as little work as possible.
+
+    Whole layers cannot balance a pipeline whose last stage also carries the LM head: for the 8B
+    shape on 8 ranks (V placement) the best whole-layer split gives two ranks 5 layers against a
+    mean of 4.28 layer-units, a 14 % loss before any bubble.  With half-layers as the unit the
+    busiest rank comes within a few percent of the mean.  Returns ``(ranges, costs)``:
+    ``ranges[s] = (first, last+1)`` in half-layer indices, ``costs[s]`` in layer units (the head's
+    ``head_units`` included in the last stage).  Local search from the proportional split:
+    move one boundary by one half-layer while that lowers (max rank load, sum of squared loads)."""
+    n_blocks = 2 * n_layers
+    assert n_stages <= n_blocks, "more stages than half-layers"
+    unit = [attention_share if b % 2 == 0 else 1.0 - attention_share for b in range(n_blocks)]
+    prefix = [0.0]
+    for u in unit:
+        prefix.append(prefix[-1] + u)
+    placement = list(placement) if placement is not None else list(range(n_stages))
+    assert len(placement) == n_stages
+
+    def stage_cost(bounds, s):
+        return prefix[bounds[s + 1]] - prefix[bounds[s]] + (head_units if s == n_stages - 1 else 0.0)
+
+    def score(bounds):
+        load = {}
+        for s in range(n_stages):
+            load[placement[s]] = load.get(placement[s], 0.0) + stage_cost(bounds, s)
+        return (round(max(load.values()), 9), round(sum(v * v for v in load.values()), 9))
+
+    n_ranks = len(set(placement))
+    is_v = n_stages == 2 * n_ranks and placement == list(range(n_ranks)) + list(range(n_ranks - 1, -1, -1))
+    bounds = _v_bottleneck_bounds(prefix, n_ranks, head_units) if is_v else None
+    if bounds is None:
+        # proportional start: stage s ends where the running cost reaches its share of the total
+        # (the head's units count towards the last stages' share)
+        total = prefix[-1] + head_units
+        per_stage = [total / n_ranks / placement.count(placement[s]) for s in range(n_stages)]
+        bounds, acc, b = [0], 0.0, 0
+        for s in range(n_stages - 1):
+            acc += per_stage[s]
+            while b < n_blocks - (n_stages - 1 - s) and prefix[b + 1] <= acc + 1e-9:
+                b += 1
+            b = max(b, bounds[-1] + 1)
+            bounds.append(b)
+        bounds.append(n_blocks)
+    # local search: shift a run of consecutive boundaries by one half-layer (a single boundary is
+    # a run of one) while that lowers (max rank load, sum of squared loads)
+    best = score(bounds)
+    improved = True
+    while improved:
+        improved = False
+        for i in range(1, n_stages):
+            for k in range(i, n_stages):
+                for step in (-1, 1):
+                    trial = list(bounds)
+                    for t in range(i, k + 1):
+                        trial[t] += step
+                    if any(trial[t] <= trial[t - 1] for t in range(1, n_stages + 1)):
+                        continue
+                    sc = score(trial)
+                    if sc < best:
+                        bounds, best, improved = trial, sc, True
+    ranges = [(bounds[s], bounds[s + 1]) for s in range(n_stages)]
+    return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
+
+
+def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float) -> Optional[List[int]]:
+    """Exact bottleneck partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th
+    range from the front and the r-th range from the back (the last one also carries the head).
+    Bisection on the bottleneck T; for a given T a sweep over the ranks keeps, for every number of
+    half-layers taken from the front, the largest number that can have been taken from the back."""
+    n, p = len(prefix) - 1, n_ranks
+    if n < 2 * p:
+        return None
+
+    def feasible(T):
+        # reach[i] = (smallest j such that ranks 0..r-1 can cover [0,i) and [j,n)), with back-pointers
+        reach = {0: (n, None)}
+        trail = []
+        for r in range(p):
+            extra = head_units if r == 0 else 0.0
+            left_after = 2 * (p - 1 - r)  # half-layers the remaining ranks need at least
+            nxt = {}
+            for i, (j, _) in reach.items():
+                for i2 in range(i + 1, j):
+                    budget = T - extra - (prefix[i2] - prefix[i])
+                    if budget < -1e-12:
+                        break
+                    if r == p - 1:
+                        j2 = i2  # the last rank's back range closes the gap exactly
+                        if j2 >= j or prefix[j] - prefix[j2] > budget + 1e-12:
+                            continue
+                    else:
+                        j2 = j - 1  # at least one half-layer, then as many as the budget allows
+                        if prefix[j] - prefix[j2] > budget + 1e-12:
+                            continue
+                        while j2 - 1 >= i2 + left_after and prefix[j] - prefix[j2 - 1] <= budget + 1e-12:
+                            j2 -= 1
+                        if j2 < i2 + left_after:
+                            continue
+                    if i2 not in nxt or j2 < nxt[i2][0]:
+                        nxt[i2] = (j2, i)
+            if not nxt:
+                return None
+            trail.append(nxt)
+            reach = nxt
+        ends = [i for i, (j, _) in reach.items() if j == i]
+        if not ends:
+            return None
+        i = ends[0]
+        front, back = [], []
+        for r in range(p - 1, -1, -1):
+            j, prev = trail[r][i]
+            front.append(i)
+            back.append(j)
+            i = prev
+        front.reverse()
+        back.reverse()
+        # boundaries: 0, front ends..., then back starts from the innermost rank outwards, n
+        return [0] + front + back[::-1][1:] + [n]
+
+    lo, hi = 0.0, prefix[-1] + head_units
+    best = feasible(hi)
+    if best is None:
+        return None
+    for _ in range(40):
+        mid = 0.5 * (lo + hi)
+        got = feasible(mid)
+        if got is None:
+            lo = mid
+        else:
+            hi, best = mid, got
+    return best
+
+
+def _modules_for_range(cfg: LlamaConfig, first: int, last: int) -> List[nn.Module]:
+    """Modules of the half-layers [first, last): whole layers where both halves are inside."""
+    mods: List[nn.Module] = []
+    b = first
+    while b < last:
+        if b % 2 == 0 and b + 1 < last:
+            mods.append(LlamaDecoderLayer(cfg))
+            b += 2
+        elif b % 2 == 0:
+            mods.append(LlamaAttentionBlock(cfg))
+            b += 1
+        else:
+            mods.append(LlamaMLPBlock(cfg))
+            b += 1
+    return mods
+
+
+def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers: bool = False) -> List[float]:
+    """Cost of every stage in decoder-layer units (LM head included), as ``build_llama_stages`` cuts them."""
+    head = head_cost_in_layers(cfg) if placement is not None else 0.0
+    if split_layers:
+        return half_layer_ranges(cfg.n_layers, n_stages, placement, head)[1]
+    counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)
+    return [c + (head_cost_in_layers(cfg) if i == n_stages - 1 else 0.0) for i, c in enumerate(counts)]
+
+
+def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False) -> List[Optional[LlamaStage]]:
     """Build the stages listed in ``only`` (all by default) directly on ``device``; the
     others are returned as ``None``, so a rank materialises only what it hosts.  Stage ``i``
     is seeded with ``seed + i``: the weights of a stage do not depend on who builds it.
-    With ``placement`` the layer counts are balanced per rank (see ``layers_per_stage``)."""
+    With ``placement`` the layer counts are balanced per rank (see ``layers_per_stage``);
+    with ``split_layers`` a stage boundary may also fall between the attention half and the
+    MLP half of a layer (see ``half_layer_ranges``)."""
     from ..zb_utils import replace_layer_with_layer_dw
 
-    counts = layers_per_stage(cfg.n_layers, n_stages, placement, head_cost_in_layers(cfg) if placement is not None else 0.0)
+    head = head_cost_in_layers(cfg) if placement is not None else 0.0
+    if split_layers:
+        ranges = half_layer_ranges(cfg.n_layers, n_stages, placement, head)[0]
+    else:
+        counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)
+        ends = [2 * sum(counts[: i + 1]) for i in range(n_stages)]
+        ranges = [(ends[i] - 2 * counts[i], ends[i]) for i in range(n_stages)]
     stages: List[Optional[LlamaStage]] = []
-    for i, n in enumerate(counts):
+    for i, (first, last) in enumerate(ranges):
         if only is not None and i not in only:
             stages.append(None)
             continue
@@ -227,7 +443,7 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
             mods: List[nn.Module] = []
             if i == 0:
                 mods.append(LlamaEmbedding(cfg))
-            mods += [LlamaDecoderLayer(cfg) for _ in range(n)]
+            mods += _modules_for_range(cfg, first, last)
             if i == n_stages - 1:
                 mods.append(LlamaHead(cfg))
             stage = LlamaStage(*mods).to(dtype)

@@ -426,17 +426,49 @@ def generate_hanayo_schedule(placement, n_micro_batches) -> List[Operation]:
     return _list_schedule(placement, n_micro_batches, split_w=False, cap=max(1, len(placement) // p) * p)
 
 
-def generate_zbv_schedule(placement, n_micro_batches, *, cap: Optional[int] = None, stage_costs: Optional[Sequence[float]] = None,
-                          ratios: Sequence[float] = (1.0, 1.0, 1.0)) -> List[Operation]:
+def generate_zbv_schedule(placement, n_micro_batches, *, cap=None, stage_costs: Optional[Sequence[float]] = None,
+                          ratios: Sequence[float] = (1.0, 1.0, 1.0), cap_limit: Optional[int] = None) -> List[Operation]:
     """ZB-V on the V placement ``[0..p-1, p-1..0]`` for any number of micro-batches.  Each
-    rank holds at most ``2p`` live (stage, micro-batch) activations — the footprint of
-    1F1B — and weight-gradient passes fill what would otherwise be bubbles.
+    rank holds at most ``cap`` live (stage, micro-batch) activations (default ``2p``, the
+    footprint of 1F1B) and weight-gradient passes fill what would otherwise be bubbles.
     ``stage_costs`` (relative weight of every stage) and ``ratios`` (F : B : W durations)
     let the schedule be laid out for stages of unequal weight; use
-    ``functools.partial(generate_zbv_schedule, stage_costs=...)`` as the scheduler."""
+    ``functools.partial(generate_zbv_schedule, stage_costs=...)`` as the scheduler.
+
+    ``cap="auto"`` lays the schedule out for several caps between ``2p`` and ``cap_limit``
+    (default ``6p``), runs each through the timeline simulator with the same costs and keeps
+    the shortest one (the smaller cap on ties): with a greedy list scheduler more live
+    activations do not always give a shorter step, so the cap is chosen by measurement."""
     p = len(set(placement))
     if len(placement) != 2 * p:
         logger.warning("zbv expects a V placement with two stages per rank, got %s", list(placement))
     cf, cb, cw = ratios
-    return _list_schedule(placement, n_micro_batches, split_w=True, cap=cap if cap is not None else 2 * p, cost_f=cf, cost_b=cb, cost_w=cw,
-                          stage_costs=stage_costs)
+
+    def build(c):
+        return _list_schedule(placement, n_micro_batches, split_w=True, cap=c, cost_f=cf, cost_b=cb, cost_w=cw, stage_costs=stage_costs)
+
+    if cap != "auto":
+        return build(cap if cap is not None else 2 * p)
+    from .simulator import simulate
+
+    costs = list(stage_costs) if stage_costs is not None else [1.0] * len(placement)
+
+    def duration(op):
+        if op.op is OperationType.FORWARD:
+            return costs[op.block_id] * cf
+        if op.op is OperationType.BACKWARD_INPUTS:
+            return costs[op.block_id] * cb
+        if op.op is OperationType.BACKWARD_PARAMS:
+            return costs[op.block_id] * cw
+        return 0.0
+
+    limit = cap_limit if cap_limit is not None else 6 * p
+    candidates = sorted({c for c in (2 * p, (5 * p) // 2, 3 * p, (7 * p) // 2, 4 * p, 5 * p, 6 * p, limit) if 2 <= c <= limit})
+    best = None
+    for c in candidates:
+        sched = build(c)
+        span = simulate(sched, list(placement), duration).makespan
+        if best is None or span < best[0] * (1.0 - 1e-6):
+            best = (span, c, sched)
+    logger.info("zbv: cap %d of %s chosen (simulated makespan %.2f)", best[1], candidates, best[0])
+    return best[2]

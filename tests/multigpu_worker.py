@@ -26,10 +26,10 @@ def rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
 
 
-def reference(cfg, n_stages, tokens, dev):
+def reference(cfg, n_stages, tokens, dev, **cut):
     """Whole model on this GPU with torch ops in fp32: loss and gradients per stage."""
-    stages = build_llama_stages(cfg, n_stages, device=dev, dtype=torch.float32, seed=7, split_backward=False)
-    bf16 = build_llama_stages(cfg, n_stages, device=dev, dtype=torch.bfloat16, seed=7, split_backward=False)
+    stages = build_llama_stages(cfg, n_stages, device=dev, dtype=torch.float32, seed=7, split_backward=False, **cut)
+    bf16 = build_llama_stages(cfg, n_stages, device=dev, dtype=torch.bfloat16, seed=7, split_backward=False, **cut)
     for s32, s16 in zip(stages, bf16):  # same (bf16-rounded) weights as the pipeline
         s32.load_state_dict({k: v.float() for k, v in s16.state_dict().items()})
     gemm.set_enabled(False)
@@ -54,6 +54,9 @@ def run(case):
         pp, dp, sched, modes = 1, world, "zbh1", ["nccl", "symm"]
     elif case == "pp":
         pp, dp, sched, modes = world, 1, "zbv", ["nccl"]
+    elif case == "pp_split":  # stage boundaries inside layers, ZB-V with the simulator-chosen activation cap
+        pp, dp, sched, modes = world, 1, "zbv", ["nccl"]
+        cfg = LlamaConfig(n_layers=5, d_model=256, n_heads=4, n_kv_heads=2, ffn=512, vocab=1024, seq_len=128, rope_theta=10000.0)
     elif case == "pp_dp":
         pp, dp, sched, modes = world // 2, 2, "1f1b", ["symm"]
     else:
@@ -63,13 +66,22 @@ def run(case):
     per_replica, nmb = 4, 4
     gen = torch.Generator().manual_seed(3)
     tokens = torch.randint(0, cfg.vocab, (dp * per_replica, cfg.seq_len + 1), generator=gen).to(dev)
-    ref_loss, ref_grads = reference(cfg, n_stages, tokens, dev)
+    cut = dict(placement=list(placement), split_layers=True) if case == "pp_split" else {}
+    scheduler = sched
+    if case == "pp_split":
+        import functools
+
+        from elf_b200.models.llama import llama_stage_costs
+        from elf_b200.scheduling.schedulers import generate_zbv_schedule
+
+        scheduler = functools.partial(generate_zbv_schedule, cap="auto", stage_costs=llama_stage_costs(cfg, n_stages, list(placement), True), ratios=(1.0, 1.25, 0.9))
+    ref_loss, ref_grads = reference(cfg, n_stages, tokens, dev, **cut)
     pp_rank, dp_rank = rank % pp, rank // pp
     mine = placement.get_ids(pp_rank)
     results = {}
     for mode in modes:
-        stages = build_llama_stages(cfg, n_stages, only=mine, device=dev, seed=7)
-        pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=sched, placement=list(placement), dp=dp, outputs="none", grad_sync=mode)
+        stages = build_llama_stages(cfg, n_stages, only=mine, device=dev, seed=7, **cut)
+        pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", grad_sync=mode)
         if mode == "symm":
             assert pipe.grad_sync is not None, "peer-memory gradient exchange was not set up"
         tok = tokens[dp_rank * per_replica : (dp_rank + 1) * per_replica]

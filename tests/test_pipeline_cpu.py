@@ -158,3 +158,45 @@ def _auto_worker(rank, world, partitioner, dp):
 @pytest.mark.parametrize("partitioner,world,dp", [("constrained", 2, 1), ("naive", 2, 1), ("dagP", 4, 2)])
 def test_auto_partition_and_model_shipping(partitioner, world, dp):
     run_ranks(_auto_worker, world, partitioner, dp)
+
+
+def _split_layer_worker(rank, world):
+    """Llama stages cut between the attention half and the MLP half of a layer, ZB-V with the
+    simulator-chosen activation cap: loss and gradients equal the same stages run in sequence."""
+    import functools
+
+    from elf_b200 import Pipeline
+    from elf_b200.models.llama import LlamaConfig, build_llama_stages, llama_loss_fn, llama_stage_costs
+    from elf_b200.scheduling.schedulers import generate_zbv_schedule
+
+    cfg = LlamaConfig(n_layers=5, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=256, seq_len=32, rope_theta=10000.0)
+    placement = list(range(world)) + list(range(world - 1, -1, -1))
+    costs = llama_stage_costs(cfg, len(placement), placement, split_layers=True)
+    ref_stages = build_llama_stages(cfg, len(placement), dtype=torch.float32, seed=11, split_backward=False, placement=placement, split_layers=True)
+    kinds = {type(m).__name__ for s in ref_stages for m in s}
+    assert {"LlamaAttentionBlock", "LlamaMLPBlock"} & kinds, kinds  # at least one layer is cut in two
+    mine = [i for i, r in enumerate(placement) if r == rank]
+    stages = build_llama_stages(cfg, len(placement), only=mine, dtype=torch.float32, seed=11, placement=placement, split_layers=True)
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, cfg.vocab, (6, cfg.seq_len + 1), generator=g)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    sched = functools.partial(generate_zbv_schedule, cap="auto", stage_costs=costs, ratios=(1.0, 1.25, 0.9))
+    pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=sched, placement=placement, outputs="device")
+    _, loss = pipe(ids, tgt, llama_loss_fn, split_size=1)
+    x = ids
+    for s in ref_stages:
+        x = s(x)
+    ref_loss = llama_loss_fn(x, tgt)
+    ref_loss.backward()
+    if pipe.is_last():
+        torch.testing.assert_close(loss, ref_loss.detach(), atol=ATOL, rtol=RTOL)
+    for block in pipe.blocks:
+        ref_params = dict(ref_stages[block.id].named_parameters())
+        for name, p in block.model.named_parameters():
+            torch.testing.assert_close(p.grad, ref_params[name.replace(".layer.", ".")].grad if name not in ref_params else ref_params[name].grad, atol=ATOL, rtol=RTOL,
+                                       msg=lambda m: f"stage {block.id} {name}: {m}")
+    pipe.clear()
+
+
+def test_stages_cut_inside_layers():
+    run_ranks(_split_layer_worker, 2)

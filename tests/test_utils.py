@@ -75,3 +75,65 @@ def _ship(rank, world):
 @pytest.mark.dist
 def test_model_shipping_between_ranks():
     run_ranks(_ship, 2)
+
+
+def test_half_layer_ranges_balance_the_head():
+    """Half-layer stage boundaries: contiguous cover, and on the V placement of the 8B shape the
+    busiest rank ends within 4 % of the mean, where whole layers leave it 17 % above."""
+    from elf_b200.models.llama import LLAMA_CONFIGS, half_layer_ranges, head_cost_in_layers, llama_stage_costs
+
+    cfg = LLAMA_CONFIGS["llama3-8b"]
+    head = head_cost_in_layers(cfg)
+    for pp in (2, 4, 8):
+        placement = list(range(pp)) + list(range(pp - 1, -1, -1))
+        ranges, costs = half_layer_ranges(cfg.n_layers, 2 * pp, placement, head)
+        assert ranges[0][0] == 0 and ranges[-1][1] == 2 * cfg.n_layers
+        assert all(a < b for a, b in ranges) and all(ranges[i][1] == ranges[i + 1][0] for i in range(2 * pp - 1))
+        assert abs(sum(costs) - (cfg.n_layers + head)) < 1e-9
+
+        def worst(c):
+            load = [0.0] * pp
+            for s, v in enumerate(c):
+                load[placement[s]] += v
+            return max(load) / (sum(load) / pp)
+
+        assert worst(costs) <= worst(llama_stage_costs(cfg, 2 * pp, placement, split_layers=False)) + 1e-9
+        if pp == 8:
+            assert worst(costs) < 1.04 and worst(llama_stage_costs(cfg, 16, placement, False)) > 1.15
+    # one stage per rank and an interleaved placement go through the local search
+    for placement in ([0, 1, 2, 3], [0, 1, 2, 3, 0, 1, 2, 3]):
+        ranges, costs = half_layer_ranges(16, len(placement), placement, 1.5)
+        assert ranges[0][0] == 0 and ranges[-1][1] == 32 and all(a < b for a, b in ranges)
+
+
+def test_split_layer_modules_equal_whole_layer():
+    import torch
+
+    from elf_b200.models.llama import LlamaAttentionBlock, LlamaConfig, LlamaDecoderLayer, LlamaMLPBlock, init_llama_
+
+    cfg = LlamaConfig(n_layers=1, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=64, seq_len=16, rope_theta=10000.0)
+    whole = init_llama_(LlamaDecoderLayer(cfg).float(), 0.1, seed=2)
+    attn, mlp = LlamaAttentionBlock(cfg).float(), LlamaMLPBlock(cfg).float()
+    attn.load_state_dict({k: v for k, v in whole.state_dict().items() if k.split(".")[0] in ("norm1", "wqkv", "wo")})
+    mlp.load_state_dict({k: v for k, v in whole.state_dict().items() if k.split(".")[0] in ("norm2", "w_gate_up", "w_down")})
+    x = torch.randn(2, 16, 64)
+    torch.testing.assert_close(mlp(attn(x)), whole(x), atol=1e-5, rtol=1e-5)
+
+
+def test_zbv_auto_cap_is_never_worse_than_fixed_caps():
+    from elf_b200.scheduling.scheduling import OperationType as T
+    from elf_b200.scheduling.schedulers import generate_zbv_schedule
+    from elf_b200.scheduling.simulator import simulate
+
+    p, n = 4, 8
+    placement = list(range(p)) + list(range(p - 1, -1, -1))
+    costs = [1.0, 1.3, 1.0, 0.7, 1.0, 1.3, 1.0, 2.1]
+    ratios = (1.0, 1.25, 0.9)
+
+    def span(sched):
+        w = {T.FORWARD: ratios[0], T.BACKWARD_INPUTS: ratios[1], T.BACKWARD_PARAMS: ratios[2]}
+        return simulate(sched, placement, lambda op: costs[op.block_id] * w.get(op.op, 0.0)).makespan
+
+    auto = span(generate_zbv_schedule(placement, n, cap="auto", stage_costs=costs, ratios=ratios))
+    for cap in (2 * p, 3 * p, 4 * p, 6 * p):
+        assert auto <= span(generate_zbv_schedule(placement, n, cap=cap, stage_costs=costs, ratios=ratios)) * (1 + 1e-6)
