@@ -324,72 +324,117 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
 
 
 def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float) -> Optional[List[int]]:
-    """Exact bottleneck partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th
-    range from the front and the r-th range from the back (the last one also carries the head).
-    Bisection on the bottleneck T; for a given T a sweep over the ranks keeps, for every number of
-    half-layers taken from the front, the largest number that can have been taken from the back."""
+    """Exact partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th range from
+    the front and the r-th range from the back (the last one also carries the head).  First the
+    smallest possible bottleneck T (busiest rank) is found by bisection; then, among the
+    partitions whose ranks all stay within T, the one with the smallest sum of squared *stage*
+    costs is taken, so that a rank's two stages are of similar size (a rank with a tiny front
+    stage and a huge back stage is balanced on paper but lengthens the pipeline's fill and
+    drain).  Both steps are a sweep over the ranks from the outside in over states
+    (half-layers taken from the front, half-layers taken from the back)."""
     n, p = len(prefix) - 1, n_ranks
     if n < 2 * p:
         return None
 
-    def feasible(T):
-        # reach[i] = (smallest j such that ranks 0..r-1 can cover [0,i) and [j,n)), with back-pointers
-        reach = {0: (n, None)}
+    def sweep(T, want_bounds, window=None):
+        # states[(i, j)] = (sum of squared stage costs so far, previous state); with a window only
+        # stages whose cost lies within `window` of T/2 are tried (the head counts for rank 0's back stage)
+        states = {(0, n): (0.0, None)}
         trail = []
         for r in range(p):
             extra = head_units if r == 0 else 0.0
             left_after = 2 * (p - 1 - r)  # half-layers the remaining ranks need at least
             nxt = {}
-            for i, (j, _) in reach.items():
+            for (i, j), (sq, _) in states.items():
+                for i2 in range(i + 1, j):
+                    front = prefix[i2] - prefix[i]
+                    budget = T - extra - front
+                    if budget < -1e-12:
+                        break
+                    if window is not None and (front < T / 2 - window or front > T / 2 + window):
+                        continue
+                    lo = i2 if r == p - 1 else i2 + left_after  # the last rank's back range closes the gap exactly
+                    hi = i2 if r == p - 1 else j - 1
+                    for j2 in range(hi, lo - 1, -1):
+                        if j2 >= j:
+                            continue
+                        back = prefix[j] - prefix[j2]
+                        if back > budget + 1e-12:
+                            break
+                        if window is not None and back + extra < T / 2 - window:
+                            continue
+                        cand = sq + front * front + (back + extra) * (back + extra)
+                        key = (i2, j2)
+                        if key not in nxt or cand < nxt[key][0] - 1e-12:
+                            nxt[key] = (cand, (i, j))
+            if not nxt:
+                return None
+            trail.append(nxt)
+            states = nxt
+        ends = [(v[0], k) for k, v in states.items() if k[0] == k[1]]
+        if not ends:
+            return None
+        if not want_bounds:
+            return True
+        _, key = min(ends)
+        front, back = [], []
+        for r in range(p - 1, -1, -1):
+            front.append(key[0])
+            back.append(key[1])
+            key = trail[r][key][1]
+        front.reverse()
+        back.reverse()
+        # boundaries: 0, the front ranges' ends, then the back ranges' starts from the innermost rank outwards, n
+        return [0] + front + back[::-1][1:] + [n]
+
+    def reachable(T):
+        # feasibility only: for every front count keep the largest back count (smallest j) reachable
+        reach = {0: n}
+        for r in range(p):
+            extra = head_units if r == 0 else 0.0
+            left_after = 2 * (p - 1 - r)
+            nxt = {}
+            for i, j in reach.items():
                 for i2 in range(i + 1, j):
                     budget = T - extra - (prefix[i2] - prefix[i])
                     if budget < -1e-12:
                         break
                     if r == p - 1:
-                        j2 = i2  # the last rank's back range closes the gap exactly
+                        j2 = i2
                         if j2 >= j or prefix[j] - prefix[j2] > budget + 1e-12:
                             continue
                     else:
-                        j2 = j - 1  # at least one half-layer, then as many as the budget allows
+                        j2 = j - 1
                         if prefix[j] - prefix[j2] > budget + 1e-12:
                             continue
                         while j2 - 1 >= i2 + left_after and prefix[j] - prefix[j2 - 1] <= budget + 1e-12:
                             j2 -= 1
                         if j2 < i2 + left_after:
                             continue
-                    if i2 not in nxt or j2 < nxt[i2][0]:
-                        nxt[i2] = (j2, i)
+                    if i2 not in nxt or j2 < nxt[i2]:
+                        nxt[i2] = j2
             if not nxt:
-                return None
-            trail.append(nxt)
+                return False
             reach = nxt
-        ends = [i for i, (j, _) in reach.items() if j == i]
-        if not ends:
-            return None
-        i = ends[0]
-        front, back = [], []
-        for r in range(p - 1, -1, -1):
-            j, prev = trail[r][i]
-            front.append(i)
-            back.append(j)
-            i = prev
-        front.reverse()
-        back.reverse()
-        # boundaries: 0, front ends..., then back starts from the innermost rank outwards, n
-        return [0] + front + back[::-1][1:] + [n]
+        return any(j == i for i, j in reach.items())
 
     lo, hi = 0.0, prefix[-1] + head_units
-    best = feasible(hi)
-    if best is None:
+    if not reachable(hi):
         return None
-    for _ in range(40):
+    for _ in range(30):
         mid = 0.5 * (lo + hi)
-        got = feasible(mid)
-        if got is None:
-            lo = mid
+        if reachable(mid):
+            hi = mid
         else:
-            hi, best = mid, got
-    return best
+            lo = mid
+    T = hi * (1.0 + 1e-9) + 1e-9
+    window = 1.0
+    while window < T:
+        got = sweep(T, True, window)
+        if got is not None:
+            return got
+        window *= 2.0
+    return sweep(T, True)
 
 
 def _modules_for_range(cfg: LlamaConfig, first: int, last: int) -> List[nn.Module]:
