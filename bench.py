@@ -97,7 +97,7 @@ def run_ours(args):
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()
 
     batch = args.nmb * args.mb_size
-    n_batches = args.warmup + 2 * args.steps
+    n_batches = args.warmup + 2 * args.steps + 1
     gen = torch.Generator().manual_seed(1000 + rank // pp)
     host = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len + 1), generator=gen).pin_memory() for _ in range(n_batches)]
 
@@ -162,6 +162,28 @@ def run_ours(args):
             "d2h_bytes_per_step": 4 if pipe.is_last() else 0,
             "wall_ms_per_step": (time.perf_counter() - t0) * 1e3 / args.steps,
         }
+    # ---- one more step, outside every timed region, with per-operation timers: bubble share ----
+    bubble = None
+    os.environ["ELF_TIMINGS"] = "1"
+    try:
+        fence()
+        step(*to_device(next(it)))
+        fence()
+        st = pipe.stats
+        mine_pct = 100.0 * st["idle"] / st["total"] if st.get("total") else 0.0
+        every = [None] * world
+        if world > 1:
+            dist.all_gather_object(every, mine_pct)
+        else:
+            every = [mine_pct]
+        bubble = {
+            "bubble_pct_mean": sum(every) / world,
+            "bubble_pct_max": max(every),
+            "per_rank": [round(v, 2) for v in every],
+            "note": "one extra step with per-operation CUDA-event timers: share of the step in which a rank runs no forward / backward / loss / optimizer-free compute operation (waiting for peers, p2p, launch gaps)",
+        }
+    finally:
+        os.environ.pop("ELF_TIMINGS", None)
     tokens = dp * batch * cfg.seq_len * args.steps
     value = tokens / (dev_ms / 1e3)
     line = {
@@ -194,6 +216,7 @@ def run_ours(args):
         "clocks": clocks.summary(),
         "e2e": e2e,
         "gpu_launches": launches,
+        "bubble": bubble,
         "peak_gb_per_gpu": peak_gb,
         "loss": last_loss,
         "host_stats_last_step": {k: round(v, 6) for k, v in stats.items()},

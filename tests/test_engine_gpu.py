@@ -1,0 +1,154 @@
+"""The engine's memory features on a GPU: rematerialisation options, activation offload through
+the pinned arena and side streams, ILP profiling with CUDA events, `memory_budget`, timing and
+memory statistics.  Single process, one GPU; numerics against the same model run plainly."""
+
+import copy
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from elf_b200.ops import _ext
+
+    assert _ext.available(), "the native extension must be built for GPU tests"
+    return torch.device("cuda", 0)
+
+
+def _gpt(dev, scheduler, placement, with_sample=False, **kw):
+    from elf_b200 import Pipeline, replace_layer_with_layer_dw
+    from elf_b200.models.gpt import GPT, GPTConfig, gpt_stages
+
+    cfg = GPTConfig(n_layers=2, d_model=128, n_heads=2, ffn=256, vocab=256, seq_len=64)
+    torch.manual_seed(0)
+    model = GPT(cfg).to(dev)
+    ref = copy.deepcopy(model)
+    stages = gpt_stages(model, len(placement))
+    for s in stages:
+        replace_layer_with_layer_dw(s)
+    g = torch.Generator().manual_seed(1)
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g).to(dev)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    pipe = Pipeline(stages, ids[:1] if with_sample else None, partitioner=False, scheduler=scheduler, placement=placement, outputs="device", **kw)
+    return pipe, ref, GPT, ids, tgt
+
+
+def _check(pipe, ref, GPT, ids, tgt, loss):
+    rl = GPT.loss_fn(ref(ids), tgt)
+    rl.backward()
+    torch.testing.assert_close(loss, rl.detach(), atol=2e-4, rtol=2e-4)
+    got = [p.grad for b in pipe.blocks for p in b.model.parameters()]
+    want = [p.grad for p in ref.parameters()]
+    assert len(got) == len(want)
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, atol=2e-4, rtol=2e-3)
+
+
+def _solution(n_stages, nmb, **tables):
+    zero = [[0] * nmb for _ in range(n_stages)]
+    sol = {"objective": 0.0, "full_fwd": copy.deepcopy(zero), "activations_bwd": copy.deepcopy(zero), "full_bwd": copy.deepcopy(zero), "offload": copy.deepcopy(zero)}
+    for name, cells in tables.items():
+        for s, j in cells:
+            sol[name][s][j] = 1
+    return sol
+
+
+@pytest.mark.parametrize(
+    "tables",
+    [
+        dict(full_fwd=[(0, 0), (1, 1)], activations_bwd=[(0, 1), (1, 2)], full_bwd=[(1, 0)]),
+        dict(offload=[(0, 0), (0, 2), (1, 1), (1, 3)]),
+        dict(full_fwd=[(0, 1)], activations_bwd=[(1, 2)], full_bwd=[(1, 0)], offload=[(0, 2), (1, 3)]),
+    ],
+)
+@pytest.mark.parametrize("base", ["1f1b", "zbv"])
+def test_remat_and_offload_options_on_gpu(dev, tables, base):
+    """Every (stage, micro-batch) option of the ILP's solution space, offload included (D2H on a
+    side stream into the pinned arena, prefetch before the backward), leaves the numbers alone."""
+    from elf_b200.registry import SCHEDULERS
+    from elf_b200.scheduling.ilp import RematScheduler
+
+    placement, nmb = [0, 0], 4
+    sched = RematScheduler(SCHEDULERS[base], _solution(2, nmb, **tables))
+    pipe, ref, GPT, ids, tgt = _gpt(dev, sched, placement)
+    for _ in range(2):  # the second step reuses the arena's blocks
+        pipe.zero_grad()
+        _, loss = pipe(ids, tgt, GPT.loss_fn, split_size=1)
+    torch.cuda.synchronize()
+    _check(pipe, ref, GPT, ids, tgt, loss)
+
+
+def test_offload_hooks_move_bytes_and_restore_them(dev):
+    from elf_b200.execution.offload import OffloadToCPU, PinnedHostTensorPool
+
+    pool = PinnedHostTensorPool(8 << 20)
+    off = OffloadToCPU(pool=pool, min_bytes=1024)
+    w = torch.randn(256, 256, device=dev, requires_grad=True)
+    x = torch.randn(512, 256, device=dev, requires_grad=True)
+    with off:
+        h = x @ w
+        y = (h * h).sum() + (h.t() * 2).sum()
+    assert off.offloaded_bytes >= h.numel() * 4
+    off.prefetch()
+    y.backward()
+    xr, wr = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    hr = xr @ wr
+    ((hr * hr).sum() + (hr.t() * 2).sum()).backward()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(x.grad, xr.grad, atol=1e-3, rtol=1e-4)
+    torch.testing.assert_close(w.grad, wr.grad, atol=1e-3, rtol=1e-4)
+    off.release()
+    assert pool.in_use == 0
+
+
+def test_ilp_profile_solve_and_train_on_gpu(dev):
+    """Profile the stages with CUDA events, tighten the budget until the solver rematerialises,
+    train with that schedule, then let `memory_budget=` drive the same machinery."""
+    from elf_b200.registry import SCHEDULERS
+    from elf_b200.scheduling.ilp import profile_all_stages, solve_remat, stagerematify
+
+    placement, nmb = [0, 0], 4
+    pipe, ref, GPT, ids, tgt = _gpt(dev, "zbv", placement)
+    stats = profile_all_stages(pipe.blocks, pipe.signatures, pipe.placement, ids[:1], None)
+    assert len(stats) == 2 and all(st["T"]["f"] > 0 and st["M"]["f"] > 0 and st["Mparams"] > 0 for st in stats)
+    free = solve_remat(stats, placement, SCHEDULERS["zbv"], nmb, 1e12, time_limit=20)
+    chosen = None
+    for frac in (0.98, 0.95, 0.92, 0.88, 0.84, 0.8, 0.75, 0.7):
+        budget = frac * max(free["peak_mems"])
+        try:
+            sol = solve_remat(stats, placement, SCHEDULERS["zbv"], nmb, budget, time_limit=20)
+        except RuntimeError:
+            break
+        if sum(map(sum, sol["full_fwd"])) + sum(map(sum, sol["activations_bwd"])) + sum(map(sum, sol["full_bwd"])) > 0:
+            chosen = budget
+            break
+    assert chosen is not None, "no budget made the solver choose a remat option"
+    pipe2, ref2, GPT, ids, tgt = _gpt(dev, stagerematify("zbv", stats, chosen), placement)
+    _, loss = pipe2(ids, tgt, GPT.loss_fn, split_size=1)
+    _check(pipe2, ref2, GPT, ids, tgt, loss)
+
+    pipe3, ref3, GPT, ids, tgt = _gpt(dev, "zbv", placement, with_sample=True, memory_budget=chosen)
+    assert len(pipe3.get_profiling_statistics()) == 2
+    _, loss = pipe3(ids, tgt, GPT.loss_fn, split_size=1)
+    _check(pipe3, ref3, GPT, ids, tgt, loss)
+
+
+def test_timing_and_memory_statistics_on_gpu(dev):
+    os.environ["ELF_TIMINGS"] = "1"
+    os.environ["ELF_MEMORY"] = "1"
+    try:
+        pipe, ref, GPT, ids, tgt = _gpt(dev, "zbh1", [0])
+        pipe(ids, tgt, GPT.loss_fn, split_size=2)
+        torch.cuda.synchronize()
+        assert set(pipe.stats) == {"total", "idle", "start_idle", "end_idle", "bubble"}
+        assert pipe.stats["total"] > 0 and pipe.stats["idle"] <= pipe.stats["total"]
+        names = set(pipe.detailed_stats["all_events"])
+        assert {"forward(0:0)", "backward_inputs(0:1)", "backward_params(0:0)", "loss_forward"} <= names
+        assert pipe.detailed_stats["peak_memory"], "ELF_MEMORY records the peak per operation"
+    finally:
+        os.environ.pop("ELF_TIMINGS")
+        os.environ.pop("ELF_MEMORY")
