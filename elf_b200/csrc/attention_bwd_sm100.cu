@@ -354,7 +354,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_const
               mbar_arrive(bar(STG_FREE + half));
             }
           }
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the leader's verdict reaches its warp
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the leader's result reaches its warp
           if (!ok) break;
         }
         if (!ok) break;

@@ -6,6 +6,11 @@
 // addresses and never calls cudaHostAlloc again.  (Behavioural counterpart of the
 // reference's Python PinnedHostTensorPool, elf/execution/offload.py:14-163.)
 #include <torch/extension.h>
+
+#include <algorithm>
+#include <deque>
+#include <limits>
+#include <vector>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -132,7 +137,54 @@ static at::Tensor host_tensor(uintptr_t addr, int64_t nbytes) {
   return at::from_blob(reinterpret_cast<void*>(addr), {nbytes}, at::TensorOptions().dtype(at::kByte).device(at::kCPU));
 }
 
+// Minimum-volume contiguous k-way cut of a topologically ordered graph (the solver behind the
+// in-tree "metis" / "dagP" partitioners).  prefix[i] = load of nodes [0, i); cost[i] = bytes that
+// cross a cut placed before node i; allowed[i] says whether a cut may be placed there; every part's
+// load stays within `cap`.  Dynamic programme over (parts closed, position) with a sliding-window
+// minimum over the admissible starts of the current part: O(n_parts * n).  Returns the n_parts - 1
+// cut positions, or an empty vector when the bound admits no solution.
+std::vector<int64_t> min_volume_cuts(const std::vector<double>& prefix, const std::vector<double>& cost, const std::vector<bool>& allowed, int64_t n_parts,
+                                     double cap) {
+  const int64_t n = (int64_t)prefix.size() - 1;
+  const double inf = std::numeric_limits<double>::infinity();
+  if (n <= 0 || n_parts <= 0 || (int64_t)cost.size() < n + 1 || (int64_t)allowed.size() < n + 1) return {};
+  std::vector<std::vector<double>> best(n_parts + 1, std::vector<double>(n + 1, inf));
+  std::vector<std::vector<int64_t>> back(n_parts + 1, std::vector<int64_t>(n + 1, -1));
+  best[0][0] = 0.0;
+  for (int64_t k = 1; k <= n_parts; ++k) {
+    std::deque<int64_t> window;  // candidate starts j with increasing best[k-1][j]
+    int64_t j_next = 0;
+    const bool last = k == n_parts;
+    for (int64_t i = 1; i <= n; ++i) {
+      for (; j_next < i; ++j_next) {
+        if (best[k - 1][j_next] < inf) {
+          while (!window.empty() && best[k - 1][window.back()] >= best[k - 1][j_next]) window.pop_back();
+          window.push_back(j_next);
+        }
+      }
+      while (!window.empty() && prefix[i] - prefix[window.front()] > cap) window.pop_front();
+      if (window.empty()) continue;
+      if (last ? i != n : !allowed[i]) continue;
+      const int64_t j = window.front();
+      best[k][i] = best[k - 1][j] + (last ? 0.0 : cost[i]);
+      back[k][i] = j;
+    }
+  }
+  if (best[n_parts][n] == inf) return {};
+  std::vector<int64_t> cuts;
+  int64_t i = n;
+  for (int64_t k = n_parts; k >= 1; --k) {
+    i = back[k][i];
+    cuts.push_back(i);
+  }
+  std::sort(cuts.begin(), cuts.end());
+  cuts.erase(cuts.begin());  // the leading 0
+  return cuts;
+}
+
 void register_host_runtime(pybind11::module_& m) {
+  m.def("min_volume_cuts", &min_volume_cuts, "minimum-volume contiguous k-way cut (dynamic programme)", py::arg("prefix"), py::arg("cost"), py::arg("allowed"),
+        py::arg("n_parts"), py::arg("cap"));
   m.def("host_tensor", &host_tensor, "view arena memory as a uint8 CPU tensor");
   py::class_<PinnedArena>(m, "PinnedArena")
       .def(py::init<size_t>(), py::arg("min_block_bytes") = size_t(64) << 20)

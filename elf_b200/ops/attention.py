@@ -2,9 +2,11 @@
 
 ``attention(q, k, v)`` takes ``q [B, S, Hq, D]`` and ``k, v [B, S, Hkv, D]`` (any strides with a
 contiguous head dim — e.g. slices of one fused QKV projection) and returns ``[B, S, Hq, D]``.
-Back ends, in order: this package's sm_100a kernel when built and applicable, else
-``torch.nn.functional.scaled_dot_product_attention`` (a library call, also what the
-reference's model zoo uses, ``benchmarks/models/simple.py:14-25,381-386``).
+Back ends: ``torch.nn.functional.scaled_dot_product_attention`` by default (a library call, also
+what the reference's model zoo uses, ``benchmarks/models/simple.py:14-25,381-386``); with
+``ELF_B200_ATTENTION=native`` the packed entry point runs this package's tcgen05 forward and
+backward kernels (``attention_native.py``), which are correct but slower than the library's on
+the benchmarked shapes.
 """
 
 from __future__ import annotations

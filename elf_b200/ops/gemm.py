@@ -39,6 +39,7 @@ __all__ = [
 _ENABLED = os.environ.get("ELF_B200_DISABLE_KERNELS", "0") != "1"
 # 0 = one CTA per 128x256 tile, 1 = CTA pairs (cta_group::2) on 256x256 tiles
 _VARIANT = int(os.environ.get("ELF_B200_GEMM_VARIANT", "1"))
+# split the tiles of the last, partly filled wave (pair kernel: along K with partial sums added in L2; 1-CTA kernel: into column strips)
 _SPLIT_TAIL = os.environ.get("ELF_B200_GEMM_SPLIT_TAIL", "1") != "0"
 _STATUS: Dict[int, torch.Tensor] = {}
 _DTYPES = (torch.bfloat16, torch.float16)

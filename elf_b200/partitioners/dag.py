@@ -31,7 +31,23 @@ __all__ = ["split_graph_min_volume"]
 _INF = float("inf")
 
 
-def _solve(prefix: List[float], cost: List[float], allowed: List[bool], n_parts: int, cap: float):
+def _native_solver():
+    """The C++ implementation of ``_solve`` (``csrc/host_runtime.cpp``) when the extension is built."""
+    try:
+        from ..ops import _ext
+
+        if _ext.available():
+            return getattr(_ext.get(), "min_volume_cuts", None)
+    except Exception:  # the extension is optional for the front-end
+        pass
+    return None
+
+
+def _solve(prefix: List[float], cost: List[float], allowed: List[bool], n_parts: int, cap: float, native: bool = True):
+    solver = _native_solver() if native else None
+    if solver is not None and cap != _INF:
+        cuts = solver(list(map(float, prefix)), list(map(float, cost)), list(map(bool, allowed)), int(n_parts), float(cap))
+        return [int(c) for c in cuts] if len(cuts) == n_parts - 1 and (n_parts > 1) else None
     n = len(prefix) - 1
     # best[k][i]: cheapest way to close k parts with the k-th ending right before node i
     best = [[_INF] * (n + 1) for _ in range(n_parts + 1)]

@@ -215,3 +215,36 @@ def test_custom_partitioner_via_registry():
         assert res.n == 2
     finally:
         PARTITIONERS.unregister("test_halves")
+
+
+def test_native_min_volume_solver_matches_python():
+    """The C++ cut solver of the host runtime returns the same cuts as the Python reference
+    implementation on random instances (and the same "no solution" verdicts)."""
+    import random
+
+    from elf_b200.partitioners import dag
+
+    if dag._native_solver() is None:
+        pytest.skip("native extension not built")
+    rng = random.Random(0)
+    for trial in range(60):
+        n = rng.randint(6, 80)
+        parts = rng.randint(2, min(8, n // 2))
+        times = [rng.choice([0.0, 0.5, 1.0, 2.0, 5.0]) for _ in range(n)]
+        prefix = [0.0]
+        for t in times:
+            prefix.append(prefix[-1] + t)
+        cost = [rng.choice([1.0, 2.0, 8.0, 64.0]) for _ in range(n + 1)]
+        allowed = [rng.random() < 0.8 for _ in range(n + 1)]
+        cap = rng.choice([1.05, 1.3, 2.0]) * prefix[-1] / parts
+        got = dag._solve(prefix, cost, allowed, parts, cap, native=True)
+        want = dag._solve(prefix, cost, allowed, parts, cap, native=False)
+        if want is None or len(want) != parts - 1:
+            assert got is None or len(got) != parts - 1
+            continue
+        assert got is not None
+        vol = lambda cuts: sum(cost[c] for c in cuts)
+        assert abs(vol(got) - vol(want)) < 1e-9  # equal optimum (ties may pick different cuts)
+        bounds = [0] + got + [n]
+        assert all(prefix[b] - prefix[a] <= cap + 1e-9 for a, b in zip(bounds, bounds[1:]))
+        assert all(allowed[c] for c in got)
