@@ -5,7 +5,8 @@
     python benchmarks/kernels.py attention   # tcgen05 flash attention forward vs the library SDPA
     python benchmarks/kernels.py fused       # bandwidth of the fused elementwise / norm / loss / optimizer kernels
     python benchmarks/kernels.py one-gemm [fwd|dx|dw] [M N K]   # a few launches of one GEMM (small case for a profiler)
-    python benchmarks/kernels.py one-attention [B S Hq Hkv]     # a few launches of the attention forward
+    python benchmarks/kernels.py one-attention [B S Hq Hkv]     # a few launches of the attention forward and backward
+    python benchmarks/kernels.py one-fused                      # a few launches of every fused bandwidth-bound kernel
 
 Timing: CUDA events on the launching stream, 3 warm-up iterations, then `--iters` timed ones.
 Variants of one op are interleaved round-robin and the median over rounds is reported, because
@@ -207,22 +208,56 @@ def one_attention(args):
 
     B, S, hq, hkv = (int(a) for a in args.rest[:4]) if len(args.rest) >= 4 else (1, 4096, 32, 8)
     qkv = torch.randn(B, S, hq + 2 * hkv, 128, device="cuda").bfloat16()
+    g = torch.randn(B, S, hq, 128, device="cuda").bfloat16()
     for _ in range(4):
-        A.forward_packed(qkv, hq, hkv)
+        out, lse = A.forward_packed(qkv, hq, hkv)
+    for _ in range(3):
+        A.backward_packed(g, qkv, out, lse, hq, hkv)
     torch.cuda.synchronize()
     G.check_status(torch.device("cuda"))
     print("done attention", B, S, hq, hkv)
 
 
+def one_fused(args):
+    """Three launches of every fused kernel on the Llama-3-8B layer shapes (operands larger than L2 where the op allows)."""
+    dev = torch.device("cuda")
+    T, D, FF, V = 4096, 4096, 14336, 32064
+    x = torch.randn(T, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gu = torch.randn(T, 2 * FF, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    logits = torch.randn(T, V, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    tgt = torch.randint(0, V, (T,), device=dev)
+    table = torch.randn(V, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, V, (1, T), device=dev)
+    qkv = torch.randn(T, 48 * 128, device=dev, dtype=torch.bfloat16)
+    cos, sin = fused.rope_tables(T, 128, 500000.0, dev)
+    n = 64 * 1024 * 1024
+    p = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    gr = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    master, m, v = p.float(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    for step in range(1, 4):
+        h, s2 = fused.add_rms_norm(x, r, w, 1e-5)
+        (h.float().sum() + s2.float().sum()).backward()
+        fused.rms_norm(x, w, 1e-5).float().sum().backward()
+        fused.swiglu(gu).float().sum().backward()
+        fused.cross_entropy(logits.clone(), tgt).backward()
+        fused.embedding(table, ids).float().sum().backward()
+        fused.rope_(qkv, cos, sin, 40, 128, T)
+        _ext.get().adamw(p, gr, master, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+    torch.cuda.synchronize()
+    print("done fused")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "attention", "fused", "one-gemm", "one-attention"])
+    ap.add_argument("what", choices=["gemm", "attention", "fused", "one-gemm", "one-attention", "one-fused"])
     ap.add_argument("rest", nargs="*")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--rounds", type=int, default=5)
     args = ap.parse_args()
     _ext.require_on_gpu()
-    {"gemm": bench_gemm, "attention": bench_attention, "fused": bench_fused, "one-gemm": one_gemm, "one-attention": one_attention}[args.what](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "fused": bench_fused, "one-gemm": one_gemm, "one-attention": one_attention, "one-fused": one_fused}[args.what](args)
 
 
 if __name__ == "__main__":
