@@ -211,3 +211,23 @@ def test_schedule_compile_is_fast():
     s = COMM_SCHEDULERS["pipelined"](s)
     assert len(s) == 3664
     assert time.perf_counter() - t0 < 2.0
+
+
+@pytest.mark.parametrize("pp", [2, 4, 8])
+def test_headline_zbv_configuration_replays_without_deadlock(pp):
+    """The schedule the benchmark runs (V placement, 16 micro-batches, stages cut inside layers for
+    the 8B shape, simulator-chosen activation cap) is valid and its p2p protocol replays on every
+    comm scheduler."""
+    from elf_b200.models.llama import LLAMA_CONFIGS, llama_stage_costs
+    from elf_b200.scheduling.schedulers import generate_zbv_schedule
+
+    placement = list(range(pp)) + list(range(pp - 1, -1, -1))
+    costs = llama_stage_costs(LLAMA_CONFIGS["llama3-8b"], 2 * pp, placement, split_layers=True)
+    sched = generate_zbv_schedule(placement, 16, cap="auto", cap_limit=6 * pp, stage_costs=costs, ratios=(1.0, 1.25, 0.9))
+    assert sum(op.op is T.FORWARD for op in sched) == 2 * pp * 16
+    assert sum(op.op is T.BACKWARD_PARAMS for op in sched) == 2 * pp * 16
+    full = add_comms(sched, sequential_signatures(placement))
+    for comm in ("topo", "pipelined"):
+        ordered = COMM_SCHEDULERS[comm](list(full))
+        check_schedule_validity(ordered)
+        replay_comms(ordered, placement)
