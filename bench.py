@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
+    ap.add_argument("--no-calibrate", action="store_true", help="keep the schedule laid out for the analytic stage costs (for comparison)")
     return ap.parse_args()
 
 
@@ -118,8 +119,22 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     it = iter(host)
-    for _ in range(args.warmup):
-        loss = step(*to_device(next(it)))
+    calibrated = None
+    for w in range(args.warmup):
+        timed_step = scheduler is not args.scheduler and not args.no_calibrate and w == min(1, args.warmup - 2) and args.warmup >= 2
+        if timed_step:
+            os.environ["ELF_TIMINGS"] = "1"
+        try:
+            loss = step(*to_device(next(it)))
+        finally:
+            os.environ.pop("ELF_TIMINGS", None)
+        if timed_step:
+            # profile-guided schedule: lay ZB-V out again for the measured F / B / W time of every
+            # stage (the analytic stage costs above are only the starting point); the remaining
+            # warm-up steps and everything timed run the re-laid schedule
+            calibrated = pipe.measured_stage_costs()
+            pipe.set_scheduler(functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=calibrated))
+            sched_note = "zbv (list-scheduled for the F / B / W time of every stage measured in a warm-up step, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
     # ---- device-timed region: inputs resident on the device -------------------------
     resident = [to_device(next(it)) for _ in range(args.steps)]
     fence()
@@ -171,15 +186,31 @@ def run_ours(args):
         fence()
         st = pipe.stats
         mine_pct = 100.0 * st["idle"] / st["total"] if st.get("total") else 0.0
+        # mean duration of F / B / W per stage hosted here, from the per-operation timers
+        import re
+
+        per_stage = {}
+        for name, secs in pipe.detailed_stats["all_events"].items():
+            m = re.match(r"(forward|backward_inputs|backward_params)\((\d+):\d+\)", name)
+            if m:
+                per_stage.setdefault(int(m.group(2)), {}).setdefault(m.group(1), []).append(secs * 1e3)
+        mine_ops = {s: [round(sum(v.get(k, [0.0])) / max(1, len(v.get(k, [0.0]))), 3) for k in ("forward", "backward_inputs", "backward_params")] for s, v in per_stage.items()}
         every = [None] * world
         if world > 1:
-            dist.all_gather_object(every, mine_pct)
+            dist.all_gather_object(every, (mine_pct, mine_ops))
         else:
-            every = [mine_pct]
+            every = [(mine_pct, mine_ops)]
+        op_ms = {}
+        for _, ops in every:
+            op_ms.update(ops)
+        every = [p for p, _ in every]
         bubble = {
             "bubble_pct_mean": sum(every) / world,
             "bubble_pct_max": max(every),
             "per_rank": [round(v, 2) for v in every],
+            "stage_op_ms_f_b_w": {str(k): op_ms[k] for k in sorted(op_ms)},
+            "stage_costs_analytic": [round(c, 2) for c in stage_costs],
+            "stage_ms_calibrated_f_b_w": [[round(1e3 * v, 3) for v in t] for t in calibrated] if calibrated else None,
             "note": "one extra step with per-operation CUDA-event timers: share of the step in which a rank runs no forward / backward / loss / optimizer-free compute operation (waiting for peers, p2p, launch gaps)",
         }
     finally:

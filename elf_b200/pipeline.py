@@ -29,7 +29,7 @@ import logging
 import os
 from dataclasses import dataclass, field, fields
 from datetime import timedelta
-from typing import Any, Callable, Iterator, List, Optional, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -382,6 +382,48 @@ class Pipeline:
 
     def is_last(self) -> bool:
         return self.placement.is_tail(self.pp_rank)
+
+    def set_scheduler(self, scheduler) -> None:
+        """Replace the scheduler (a registry key or a callable ``(placement, nmb) -> schedule``);
+        the schedule is regenerated on the next step."""
+        self.scheduler = resolve(scheduler, SCHEDULERS)
+        self.last_nmb = None
+
+    def measured_stage_costs(self):
+        """Mean measured duration, in seconds, of the forward, backward-inputs and backward-params
+        operations of every stage of the pipeline during the last step, as a list of
+        ``(f, b, w)`` triples indexed by stage — the same on every rank of the pipeline.
+
+        The last step must have run with per-operation timers (``ELF_TIMINGS=1``).  Meant for
+        profile-guided schedules: feed the list to a cost-aware scheduler such as
+        ``functools.partial(generate_zbv_schedule, cap="auto", stage_costs=costs)`` and install
+        it with ``set_scheduler``.  Stages without split backward report ``w = 0``."""
+        import re
+
+        events = (self.detailed_stats or {}).get("all_events") or {}
+        if not events:
+            raise RuntimeError("no per-operation timings: run a step with ELF_TIMINGS=1 first")
+        acc: Dict[int, Dict[str, List[float]]] = {}
+        for name, secs in events.items():
+            m = re.match(r"(forward|backward_inputs|backward_params)\((\d+):\d+\)$", name)
+            if m:
+                acc.setdefault(int(m.group(2)), {}).setdefault(m.group(1), []).append(float(secs))
+        mine = {}
+        for stage, kinds in acc.items():
+            mean = lambda k: (sum(kinds[k]) / len(kinds[k])) if kinds.get(k) else 0.0
+            mine[stage] = (mean("forward"), mean("backward_inputs"), mean("backward_params"))
+        parts = [mine]
+        if self.pp_group is not None and dist.is_initialized() and dist.get_world_size(self.pp_group) > 1:
+            parts = [None] * dist.get_world_size(self.pp_group)
+            dist.all_gather_object(parts, mine, group=self.pp_group)
+        merged: Dict[int, tuple] = {}
+        for part in parts:
+            merged.update(part)
+        n_stages = len(self.placement)
+        missing = [s for s in range(n_stages) if s not in merged]
+        if missing:
+            raise RuntimeError(f"no timings for stages {missing}")
+        return [merged[s] for s in range(n_stages)]
 
     def get_profiling_statistics(self):
         if not self._remat_stats:

@@ -311,8 +311,20 @@ def _list_schedule(
     elif isinstance(cap, int):
         cap = {r: cap for r in ranks}
     cap = dict(cap)
-    weight = [1.0] * n_stages if stage_costs is None else [float(c) for c in stage_costs]
-    assert len(weight) == n_stages, "one cost per stage"
+    if stage_costs is None:
+        stage_costs = [1.0] * n_stages
+    assert len(stage_costs) == n_stages, "one cost per stage"
+    # an entry is either a relative weight (multiplied by cost_f / cost_b / cost_w) or a measured
+    # (forward, backward-inputs, backward-params) triple of durations that is taken as it is
+    dur_f, dur_b, dur_w = [], [], []
+    for c in stage_costs:
+        if isinstance(c, (tuple, list)):
+            f, b, w = (float(x) for x in c)
+        else:
+            f, b, w = cost_f * float(c), cost_b * float(c), cost_w * float(c)
+        dur_f.append(f)
+        dur_b.append(b)
+        dur_w.append(w)
 
     UNSET = None
     f_end: List[List[Optional[float]]] = [[UNSET] * n for _ in range(n_stages)]
@@ -364,13 +376,13 @@ def _list_schedule(
             mb = b_next[s]
             out.B(s, mb)
             b_next[s] += 1
-            dur = cost_b * weight[s]
+            dur = dur_b[s]
             done += 1
             b_end[s][mb] = t + dur
             if not split_w:
                 out.W(s, mb)
                 w_next[s] += 1
-                dur += cost_w * weight[s]
+                dur += dur_w[s]
                 done += 1
             free_at[r] = t + dur
             stalled_rounds = 0
@@ -383,7 +395,7 @@ def _list_schedule(
             mb = f_next[s]
             out.F(s, mb)
             f_next[s] += 1
-            f_end[s][mb] = t + cost_f * weight[s]
+            f_end[s][mb] = t + dur_f[s]
             free_at[r] = f_end[s][mb]
             done += 1
             stalled_rounds = 0
@@ -394,7 +406,7 @@ def _list_schedule(
                 s = min(cand_w, key=lambda s: (w_next[s], s))
                 out.W(s, w_next[s])
                 w_next[s] += 1
-                free_at[r] = t + cost_w * weight[s]
+                free_at[r] = t + dur_w[s]
                 done += 1
                 stalled_rounds = 0
                 continue
@@ -433,7 +445,10 @@ def generate_zbv_schedule(placement, n_micro_batches, *, cap=None, stage_costs: 
     footprint of 1F1B) and weight-gradient passes fill what would otherwise be bubbles.
     ``stage_costs`` (relative weight of every stage) and ``ratios`` (F : B : W durations)
     let the schedule be laid out for stages of unequal weight; use
-    ``functools.partial(generate_zbv_schedule, stage_costs=...)`` as the scheduler.
+    ``functools.partial(generate_zbv_schedule, stage_costs=...)`` as the scheduler.  An entry
+    of ``stage_costs`` may also be a measured ``(forward, backward-inputs, backward-params)``
+    triple of durations (see ``Pipeline.measured_stage_costs``); ``ratios`` is then ignored
+    for that stage.
 
     ``cap="auto"`` lays the schedule out for several caps between ``2p`` and ``cap_limit``
     (default ``6p``), runs each through the timeline simulator with the same costs and keeps
@@ -452,15 +467,14 @@ def generate_zbv_schedule(placement, n_micro_batches, *, cap=None, stage_costs: 
     from .simulator import simulate
 
     costs = list(stage_costs) if stage_costs is not None else [1.0] * len(placement)
+    which = {OperationType.FORWARD: 0, OperationType.BACKWARD_INPUTS: 1, OperationType.BACKWARD_PARAMS: 2}
 
     def duration(op):
-        if op.op is OperationType.FORWARD:
-            return costs[op.block_id] * cf
-        if op.op is OperationType.BACKWARD_INPUTS:
-            return costs[op.block_id] * cb
-        if op.op is OperationType.BACKWARD_PARAMS:
-            return costs[op.block_id] * cw
-        return 0.0
+        k = which.get(op.op)
+        if k is None:
+            return 0.0
+        c = costs[op.block_id]
+        return float(c[k]) if isinstance(c, (tuple, list)) else float(c) * (cf, cb, cw)[k]
 
     limit = cap_limit if cap_limit is not None else 6 * p
     candidates = sorted({c for c in (2 * p, (5 * p) // 2, 3 * p, (7 * p) // 2, 4 * p, 5 * p, 6 * p, limit) if 2 <= c <= limit})

@@ -195,6 +195,27 @@ def _split_layer_worker(rank, world):
         for name, p in block.model.named_parameters():
             torch.testing.assert_close(p.grad, ref_params[name.replace(".layer.", ".")].grad if name not in ref_params else ref_params[name].grad, atol=ATOL, rtol=RTOL,
                                        msg=lambda m: f"stage {block.id} {name}: {m}")
+    # profile-guided re-layout: time one step per operation, lay the schedule out again for the
+    # measured (F, B, W) durations of every stage, and get the same numbers from the new schedule
+    import os
+
+    os.environ["ELF_TIMINGS"] = "1"
+    try:
+        pipe.zero_grad()
+        pipe(ids, tgt, llama_loss_fn, split_size=1)
+    finally:
+        os.environ.pop("ELF_TIMINGS")
+    measured = pipe.measured_stage_costs()
+    assert len(measured) == len(placement) and all(len(t) == 3 and t[0] > 0 and t[1] > 0 and t[2] > 0 for t in measured)
+    pipe.set_scheduler(functools.partial(generate_zbv_schedule, cap="auto", stage_costs=measured))
+    pipe.zero_grad()
+    _, loss2 = pipe(ids, tgt, llama_loss_fn, split_size=1)
+    if pipe.is_last():
+        torch.testing.assert_close(loss2, ref_loss.detach(), atol=ATOL, rtol=RTOL)
+    for block in pipe.blocks:
+        ref_params = dict(ref_stages[block.id].named_parameters())
+        for name, p in block.model.named_parameters():
+            torch.testing.assert_close(p.grad, ref_params[name.replace(".layer.", ".")].grad if name not in ref_params else ref_params[name].grad, atol=ATOL, rtol=RTOL)
     pipe.clear()
 
 
