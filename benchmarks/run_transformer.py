@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument("--opt-device", default="cuda", choices=["cpu", "cuda"])
     ap.add_argument("--no-optimizer", action="store_true")
     ap.add_argument("--partitioner", default="handcrafted", choices=["naive", "constrained", "metis", "dagP", "handcrafted"])
+    ap.add_argument("--split-layers", action="store_true", help="llama: let stage boundaries fall between the attention half and the MLP half of a layer")
     ap.add_argument("--scheduler", default="1f1b", choices=["gpipe", "afab", "1f1b", "megatron", "hanayo", "zbh1", "zbh2", "zbv", "full_remat", "file", "auto"])
     ap.add_argument("--schedule-file")
     ap.add_argument("--interleaving", type=int, default=1)
@@ -123,7 +124,17 @@ def main():
     if args.architecture == "llama":
         cfg = LLAMA_CONFIGS[args.model]
         mine = placement.get_ids(pp_rank)
-        stages = build_llama_stages(cfg, len(placement), only=mine, device=device, dtype=dtype, seed=1234, placement=list(placement))
+        stages = build_llama_stages(cfg, len(placement), only=mine, device=device, dtype=dtype, seed=1234, placement=list(placement), split_layers=args.split_layers)
+        if args.scheduler == "zbv" and pp > 1 and not args.checkpointing and not args.offloading and args.memory_budget is None:
+            # ZB-V laid out for what the stages cost (layer halves per stage, LM head on the last one),
+            # with the live-activation cap chosen by the timeline simulator
+            import functools
+
+            from elf_b200.models.llama import llama_stage_costs
+            from elf_b200.scheduling.schedulers import generate_zbv_schedule
+
+            scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, ratios=(1.0, 1.4, 0.85),
+                                          stage_costs=llama_stage_costs(cfg, len(placement), list(placement), args.split_layers))
         parts, signatures, partitioner = [stages[i] for i in mine], sequential_signatures(placement), False
         loss_fn, vocab, seq = llama_loss_fn, cfg.vocab, cfg.seq_len
         sample = torch.randint(0, vocab, (args.mb_size, seq), device=device)
