@@ -43,6 +43,39 @@ def test_gemm_family(dev, m, n, k):
     G.check_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 5120, 1024), (4000, 5064, 1000), (3900, 4872, 520)])
+def test_gemm_k_split_tail(dev, m, n, k):
+    """Shapes with more tiles than CTA pairs and a small last wave: the pair kernel splits that wave
+    along K and adds the partial sums in L2.  Ragged rows / columns / K, bias, accumulation and an
+    output with a row pitch larger than its width (the pre-clearing then runs as a 2-D memset)."""
+    from elf_b200.ops import _ext
+    from elf_b200.ops import gemm as G
+
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    dy = torch.randn(m, n, device=dev, dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for split in (True, False):
+        G.set_variant(1, split)
+        try:
+            assert rel_err(G.linear_forward(x, w), ref) < 5e-3
+            assert rel_err(G.linear_forward(x, w, bias), ref + bias.float()) < 5e-3
+            assert rel_err(G.linear_input_grad(dy, w), dy.float() @ w.float()) < 5e-3
+            acc = torch.full((n, k), 0.25, device=dev, dtype=torch.float32)
+            G.linear_weight_grad(dy, x, out=acc)
+            assert rel_err(acc, dy.float().t() @ x.float() + 0.25) < 1e-4
+            # strided output: a [m, n] window of a wider buffer whose other columns must stay untouched
+            wide = torch.full((m, n + 64), 7.0, device=dev, dtype=torch.bfloat16)
+            _ext.get().gemm(x, w, wide[:, :n], None, False, False, False, 1.0, G.status(dev), 1, split)
+            assert rel_err(wide[:, :n], ref) < 5e-3
+            assert bool((wide[:, n:] == 7.0).all())
+        finally:
+            G.set_variant(1, True)
+    G.check_status(dev)
+
+
 def test_gemm_fp16_and_strided(dev):
     from elf_b200.ops import gemm as G
 
