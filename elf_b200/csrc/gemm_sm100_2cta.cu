@@ -40,7 +40,7 @@ constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of the B 
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 4;  // in units of 256-row pair tiles
+constexpr int DEFAULT_GROUP_M = 4;  // tile rows (of 256) that are swept together before moving to the next columns
 constexpr int STAGING_BYTES = 2 * 16384;  // two 128-row x 128-byte chunks for the TMA-store epilogue
 constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + STAGING_BYTES + 1024 + 256;
 
@@ -62,11 +62,12 @@ struct WorkUnit {
 // different pairs and add their partial sums to D (TMA add-reduce in L2).  Unlike a split
 // along N this keeps the 256x256 tile's ratio of MMA work to bytes loaded.
 struct Schedule {
-  int tiles_m, tiles_n, full_tiles, ksplit, total_units;
+  int tiles_m, tiles_n, full_tiles, ksplit, total_units, group_m;
 };
 
-__host__ __device__ inline Schedule make_schedule(int M, int N, int k_blocks, int num_pairs, int max_split) {
+__host__ __device__ inline Schedule make_schedule(int M, int N, int k_blocks, int num_pairs, int max_split, int group_m) {
   Schedule s;
+  s.group_m = group_m;
   s.tiles_m = (M + 2 * BM - 1) / (2 * BM);
   s.tiles_n = (N + BN - 1) / BN;
   const int tiles = s.tiles_m * s.tiles_n;
@@ -90,10 +91,10 @@ __host__ __device__ inline Schedule make_schedule(int M, int N, int k_blocks, in
 }
 
 __host__ __device__ inline void tile_coords(int tile, const Schedule& s, int* m, int* n) {
-  const int per_group = GROUP_M * s.tiles_n;
+  const int per_group = s.group_m * s.tiles_n;
   const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int rows = (s.tiles_m - first_m) < GROUP_M ? (s.tiles_m - first_m) : GROUP_M;
+  const int first_m = group * s.group_m;
+  const int rows = (s.tiles_m - first_m) < s.group_m ? (s.tiles_m - first_m) : s.group_m;
   const int in_group = tile - group * per_group;
   *m = first_m + in_group % rows;
   *n = in_group / rows;
@@ -126,7 +127,7 @@ template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_d, void* __restrict__ d_ptr, const void* __restrict__ bias_ptr, int M, int N, int K, long long ldd,
-                         uint32_t fmt, float alpha, int max_split, int* __restrict__ status, const __grid_constant__ PushTarget push,
+                         uint32_t fmt, float alpha, int max_split, int group_m, int* __restrict__ status, const __grid_constant__ PushTarget push,
                          const __grid_constant__ PeerMaps peer_maps) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -148,7 +149,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int k_blocks = (K + BK - 1) / BK;
-  const Schedule sched = make_schedule(M, N, k_blocks, num_pairs, max_split);
+  const Schedule sched = make_schedule(M, N, k_blocks, num_pairs, max_split, group_m);
   const int num_units = sched.total_units;
 
   if (threadIdx.x == 0) {
@@ -450,7 +451,12 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   if (tiles < pairs) pairs = tiles;
   // a pushing launch stores finished sums; partial sums of a K-split tile cannot be pushed
   const int max_split = (!g.split_tail || g.push.n_peers > 0) ? 1 : 4;
-  const Schedule sched = make_schedule(g.M, g.N, (g.K + BK - 1) / BK, pairs, max_split);
+  static const int group_m = [] {
+    const char* e = getenv("ELF_B200_GEMM_GROUP_M");
+    const int v = e ? atoi(e) : DEFAULT_GROUP_M;
+    return v >= 1 && v <= 64 ? v : DEFAULT_GROUP_M;
+  }();
+  const Schedule sched = make_schedule(g.M, g.N, (g.K + BK - 1) / BK, pairs, max_split, group_m);
   if (sched.ksplit > 1 && !g.accumulate) {
     // K-split tiles add their partial sums to D, so D must start at zero there.  The split
     // tiles are the last ones of the tile order, all inside the row band that starts at the
@@ -458,7 +464,7 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
     // whole tiles that share it are stored afterwards and simply overwrite the zeros).
     int m, n;
     tile_coords(sched.full_tiles, sched, &m, &n);
-    const long long row_start = (long long)(m / GROUP_M) * GROUP_M * 2 * BM;
+    const long long row_start = (long long)(m / group_m) * group_m * 2 * BM;
     const size_t esz = g.out_f32 ? 4 : 2;
     char* base = static_cast<char*>(g.d) + size_t(row_start) * size_t(g.ldd) * esz;
     const size_t rows = size_t(g.M - row_start);
@@ -472,7 +478,7 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
     if (make_tmap_out(&peers.m[p], g.push.peer_out[p], g.out_f32 ? 2 : g.fmt, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldd, g.out_f32 ? 32 : 64, BM) != nullptr)
       return cudaErrorInvalidValue;
   }
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, g.status, g.push, peers);
+  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, group_m, g.status, g.push, peers);
   return cudaGetLastError();
 }
 
