@@ -236,3 +236,23 @@ def test_stats_and_inference():
     assert loss is None and len(out) == 2 and out[0].shape == (2, CFG.seq_len, CFG.vocab)
     pipe.zero_grad()
     assert all(p.grad is None for p in pipe.parameters())
+
+
+def test_measured_stage_costs_needs_a_timed_step():
+    pipe, _ = make("zbv", [0, 0])
+    ids, tgt = data()
+    pipe(ids, tgt, GPT.loss_fn, split_size=1)
+    with pytest.raises(RuntimeError, match="ELF_TIMINGS"):
+        pipe.measured_stage_costs()
+    os.environ["ELF_TIMINGS"] = "1"
+    try:
+        pipe.zero_grad()
+        pipe(ids, tgt, GPT.loss_fn, split_size=1)
+    finally:
+        os.environ.pop("ELF_TIMINGS")
+    costs = pipe.measured_stage_costs()
+    assert len(costs) == 2 and all(f > 0 and b > 0 and w > 0 for f, b, w in costs)
+    pipe.set_scheduler("1f1b")
+    pipe.zero_grad()
+    _, loss = pipe(ids, tgt, GPT.loss_fn, split_size=1)
+    assert torch.isfinite(loss)
