@@ -148,6 +148,9 @@ def run_ours(args):
         end.record()
         fence()
     dev_ms = max_over_ranks(start.elapsed_time(end), device)
+    from elf_b200.ops import gemm as _gemm
+
+    _gemm.check_status(device)  # a kernel that gave up on a bounded wait must not pass as a fast step
     launches = _ext.launches() - launches0
     stats = dict(pipe.stats)
     peak_gb = max_over_ranks(torch.cuda.max_memory_allocated() / 2**30, device)
