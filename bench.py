@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
+    ap.add_argument("--split-thirds", action="store_true", help="also allow a stage boundary after the MLP's SwiGLU (two tensors cross it); finer balance for deep pipelines")
     ap.add_argument("--no-calibrate", action="store_true", help="keep the schedule laid out for the analytic stage costs (for comparison)")
     return ap.parse_args()
 
@@ -54,7 +55,7 @@ def run_ours(args):
 
     from benchmarks.benchmark_utils import ClockSampler, init_dist, max_over_ranks
     from elf_b200 import Pipeline, Placement
-    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, half_layer_ranges, head_cost_in_layers, llama_loss_fn, llama_stage_costs
+    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, head_cost_in_layers, llama_loss_fn, llama_stage_costs, llama_stage_ranges, llama_stage_signatures
     from elf_b200.ops import _ext
     from elf_b200.optim import DummyOptimizer, FusedAdamW
     from dataclasses import replace
@@ -74,14 +75,13 @@ def run_ours(args):
     mine = placement.get_ids(pp_rank)
     # stage boundaries may fall between the attention half and the MLP half of a layer: whole
     # layers cannot balance 32 layers + the LM head (2.2 layers' worth) over 8 ranks
-    split_layers = pp > 1 and not args.whole_layers
+    split_layers = False if (pp == 1 or args.whole_layers) else ("thirds" if args.split_thirds else True)
     stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement), split_layers=split_layers)
     parts = [stages[i] for i in mine]
     stage_costs = llama_stage_costs(cfg, len(placement), list(placement), split_layers)
-    if split_layers:
-        counts = [(b - a) / 2 for a, b in half_layer_ranges(cfg.n_layers, len(placement), list(placement), head_cost_in_layers(cfg))[0]]
-    else:
-        counts = [round(c - (head_cost_in_layers(cfg) if i == len(placement) - 1 else 0.0)) for i, c in enumerate(stage_costs)]
+    signatures = llama_stage_signatures(cfg, len(placement), list(placement), split_layers)
+    ranges, parts_per_layer, _ = llama_stage_ranges(cfg, len(placement), list(placement), split_layers)
+    counts = [round((b - a) / parts_per_layer, 2) for a, b in ranges]
     scheduler, sched_note = args.scheduler, args.scheduler
     if args.scheduler == "zbv" and pp > 1:
         # ZB-V laid out for what the stages cost: layer counts differ per stage, the last stage
@@ -93,7 +93,7 @@ def run_ours(args):
 
         scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
         sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
-    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none")
+    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", signatures=signatures)
     params = list(pipe.parameters())
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()
 

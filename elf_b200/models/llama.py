@@ -178,6 +178,34 @@ class LlamaMLPBlock(nn.Module):
         return x + self.w_down(_f.swiglu(self.w_gate_up(self.norm2(x))))
 
 
+class LlamaMLPUpBlock(nn.Module):
+    """First part of the MLP half (norm, gate/up projection, SwiGLU).  Returns the residual stream
+    and the activation: a stage boundary after this block carries two tensors."""
+
+    _elf_leaf = True
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.norm2 = RMSNorm(cfg.d_model, cfg.eps)
+        self.w_gate_up = nn.Linear(cfg.d_model, 2 * cfg.ffn, bias=False)
+
+    def forward(self, x):
+        return x, _f.swiglu(self.w_gate_up(self.norm2(x)))
+
+
+class LlamaMLPDownBlock(nn.Module):
+    """Second part of the MLP half: down projection of the activation added to the residual stream."""
+
+    _elf_leaf = True
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.w_down = nn.Linear(cfg.ffn, cfg.d_model, bias=False)
+
+    def forward(self, x, act):
+        return x + self.w_down(act)
+
+
 class LlamaHead(nn.Module):
     _elf_leaf = True
 
@@ -191,7 +219,20 @@ class LlamaHead(nn.Module):
 
 
 class LlamaStage(nn.Sequential):
-    """A contiguous run of the model: [embedding] + decoder layers + [head]."""
+    """A contiguous run of the model: [embedding] + decoder layers (or parts of layers) + [head]."""
+
+
+class LlamaTupleStage(LlamaStage):
+    """A stage that holds a gate/up or a down block: a module that returns a tuple hands every
+    element to the next module as its own argument, and the stage itself may take or return two
+    tensors.  (A class of its own so that plain stages keep ``nn.Sequential``'s single-argument
+    forward, which the graph tracers rely on.)"""
+
+    def forward(self, *args):
+        x = args if len(args) > 1 else args[0]
+        for module in self:
+            x = module(*x) if isinstance(x, tuple) else module(x)
+        return x
 
 
 def init_llama_(module: nn.Module, std: float = 0.02, seed: Optional[int] = None) -> nn.Module:
@@ -264,7 +305,12 @@ def layers_per_stage(n_layers: int, n_stages: int, placement: Optional[Sequence[
 ATTENTION_SHARE = 0.2  # measured share of a decoder layer's forward+backward time spent in its attention half (8B shape, B200)
 
 
-def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0, attention_share: float = ATTENTION_SHARE):
+# (attention, gate/up + SwiGLU, down) shares of a layer's time when the MLP half is cut once more
+THIRD_SHARES = (ATTENTION_SHARE, 0.55, 0.25)
+
+
+def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0, attention_share: float = ATTENTION_SHARE,
+                      shares: Optional[Sequence[float]] = None):
     """Split the 2·n_layers half-layers (attention half, MLP half, attention half, ...) into
     ``n_stages`` contiguous ranges so that the busiest *rank* has as little work as possible.
 
@@ -274,10 +320,15 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     busiest rank comes within a few percent of the mean.  Returns ``(ranges, costs)``:
     ``ranges[s] = (first, last+1)`` in half-layer indices, ``costs[s]`` in layer units (the head's
     ``head_units`` included in the last stage).  Local search from the proportional split:
-    move one boundary by one half-layer while that lowers (max rank load, sum of squared loads)."""
-    n_blocks = 2 * n_layers
-    assert n_stages <= n_blocks, "more stages than half-layers"
-    unit = [attention_share if b % 2 == 0 else 1.0 - attention_share for b in range(n_blocks)]
+    move one boundary by one half-layer while that lowers (max rank load, sum of squared loads).
+    ``shares`` generalises the unit: a layer is cut into ``len(shares)`` consecutive parts of those
+    relative costs (``THIRD_SHARES`` = attention, gate/up + SwiGLU, down projection) and the
+    ranges index those parts."""
+    shares = tuple(shares) if shares is not None else (attention_share, 1.0 - attention_share)
+    k = len(shares)
+    n_blocks = k * n_layers
+    assert n_stages <= n_blocks, "more stages than layer parts"
+    unit = [shares[b % k] for b in range(n_blocks)]
     prefix = [0.0]
     for u in unit:
         prefix.append(prefix[-1] + u)
@@ -330,7 +381,7 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
 
 
-def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float) -> Optional[List[int]]:
+def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, window: float = 1.0) -> Optional[List[int]]:
     """Exact partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th range from
     the front and the r-th range from the back (the last one also carries the head).  First the
     smallest possible bottleneck T (busiest rank) is found by bisection; then, among the
@@ -435,7 +486,6 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float) -
         else:
             lo = mid
     T = hi * (1.0 + 1e-9) + 1e-9
-    window = 1.0
     while window < T:
         got = sweep(T, True, window)
         if got is not None:
@@ -444,30 +494,73 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float) -
     return sweep(T, True)
 
 
-def _modules_for_range(cfg: LlamaConfig, first: int, last: int) -> List[nn.Module]:
-    """Modules of the half-layers [first, last): whole layers where both halves are inside."""
+def _modules_for_range(cfg: LlamaConfig, first: int, last: int, k: int = 2) -> List[nn.Module]:
+    """Modules of the layer parts [first, last) (k parts per layer): whole layers, and a whole MLP
+    half, stay one fused module where all of their parts are inside."""
     mods: List[nn.Module] = []
     b = first
     while b < last:
-        if b % 2 == 0 and b + 1 < last:
+        part = b % k
+        if part == 0 and b + k <= last:
             mods.append(LlamaDecoderLayer(cfg))
-            b += 2
-        elif b % 2 == 0:
+            b += k
+        elif part == 0:
             mods.append(LlamaAttentionBlock(cfg))
             b += 1
-        else:
+        elif k == 2 or (part == 1 and b + 2 <= last):
             mods.append(LlamaMLPBlock(cfg))
+            b += k - 1
+        elif part == 1:
+            mods.append(LlamaMLPUpBlock(cfg))
+            b += 1
+        else:
+            mods.append(LlamaMLPDownBlock(cfg))
             b += 1
     return mods
 
 
-def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers: bool = False) -> List[float]:
-    """Cost of every stage in decoder-layer units (LM head included), as ``build_llama_stages`` cuts them."""
+def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers):
+    """(ranges, parts per layer, costs) for ``split_layers`` = False, True / "halves" or "thirds"."""
     head = head_cost_in_layers(cfg) if placement is not None else 0.0
-    if split_layers:
-        return half_layer_ranges(cfg.n_layers, n_stages, placement, head)[1]
+    if split_layers in (True, "halves"):
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head)
+        return ranges, 2, costs
+    if split_layers == "thirds":
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=THIRD_SHARES)
+        return ranges, 3, costs
+    assert not split_layers, f"split_layers must be False, True, 'halves' or 'thirds', got {split_layers!r}"
     counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)
-    return [c + (head_cost_in_layers(cfg) if i == n_stages - 1 else 0.0) for i, c in enumerate(counts)]
+    ends = [2 * sum(counts[: i + 1]) for i in range(n_stages)]
+    ranges = [(ends[i] - 2 * counts[i], ends[i]) for i in range(n_stages)]
+    return ranges, 2, [c + (head_cost_in_layers(cfg) if i == n_stages - 1 else 0.0) for i, c in enumerate(counts)]
+
+
+def llama_stage_ranges(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False):
+    """``(ranges, parts per layer, stage costs)`` of the cut ``build_llama_stages`` makes: ``ranges[s]`` is
+    the half-open range of layer parts of stage ``s`` (2 parts per layer, 3 with ``"thirds"``)."""
+    return _stage_ranges(cfg, n_stages, placement, split_layers)
+
+
+def llama_stage_signatures(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False):
+    """Signatures of the stages ``build_llama_stages`` cuts: one tensor per boundary, except after a
+    gate/up block (``split_layers="thirds"``), where the residual stream and the activation cross."""
+    from ..partitioners.signature import Signature
+
+    ranges, k, _ = _stage_ranges(cfg, n_stages, placement, split_layers)
+    width = [2 if (k == 3 and last % 3 == 2 and s != n_stages - 1) else 1 for s, (_, last) in enumerate(ranges)]  # tensors leaving stage s
+    sigs = []
+    for s in range(n_stages):
+        n_in = 1 if s == 0 else width[s - 1]
+        n_out = 1 if s == n_stages - 1 else width[s]
+        ins = ["input"] if n_in == 1 else ["input", "input_act"]
+        outs = ["output"] if n_out == 1 else ["output", "output_act"]
+        sigs.append(Signature(ins, outs, [s - 1 if s else None] * n_in, [[s + 1 if s != n_stages - 1 else None]] * n_out))
+    return sigs
+
+
+def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False) -> List[float]:
+    """Cost of every stage in decoder-layer units (LM head included), as ``build_llama_stages`` cuts them."""
+    return _stage_ranges(cfg, n_stages, placement, split_layers)[2]
 
 
 def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False) -> List[Optional[LlamaStage]]:
@@ -476,16 +569,12 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
     is seeded with ``seed + i``: the weights of a stage do not depend on who builds it.
     With ``placement`` the layer counts are balanced per rank (see ``layers_per_stage``);
     with ``split_layers`` a stage boundary may also fall between the attention half and the
-    MLP half of a layer (see ``half_layer_ranges``)."""
+    MLP half of a layer (see ``half_layer_ranges``), with ``split_layers="thirds"`` also after the
+    MLP's SwiGLU, where two tensors cross the boundary (pass ``llama_stage_signatures(...)`` to the
+    pipeline in that case)."""
     from ..zb_utils import replace_layer_with_layer_dw
 
-    head = head_cost_in_layers(cfg) if placement is not None else 0.0
-    if split_layers:
-        ranges = half_layer_ranges(cfg.n_layers, n_stages, placement, head)[0]
-    else:
-        counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)
-        ends = [2 * sum(counts[: i + 1]) for i in range(n_stages)]
-        ranges = [(ends[i] - 2 * counts[i], ends[i]) for i in range(n_stages)]
+    ranges, parts_per_layer, _ = _stage_ranges(cfg, n_stages, placement, split_layers)
     stages: List[Optional[LlamaStage]] = []
     for i, (first, last) in enumerate(ranges):
         if only is not None and i not in only:
@@ -495,10 +584,11 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
             mods: List[nn.Module] = []
             if i == 0:
                 mods.append(LlamaEmbedding(cfg))
-            mods += _modules_for_range(cfg, first, last)
+            mods += _modules_for_range(cfg, first, last, parts_per_layer)
             if i == n_stages - 1:
                 mods.append(LlamaHead(cfg))
-            stage = LlamaStage(*mods).to(dtype)
+            tupled = any(isinstance(m, (LlamaMLPUpBlock, LlamaMLPDownBlock)) for m in mods)
+            stage = (LlamaTupleStage if tupled else LlamaStage)(*mods).to(dtype)
         init_llama_(stage, cfg.init_std, seed + i)
         if split_backward:
             replace_layer_with_layer_dw(stage)

@@ -160,32 +160,36 @@ def test_auto_partition_and_model_shipping(partitioner, world, dp):
     run_ranks(_auto_worker, world, partitioner, dp)
 
 
-def _split_layer_worker(rank, world):
+def _split_layer_worker(rank, world, mode=True):
     """Llama stages cut between the attention half and the MLP half of a layer, ZB-V with the
     simulator-chosen activation cap: loss and gradients equal the same stages run in sequence."""
     import functools
 
     from elf_b200 import Pipeline
-    from elf_b200.models.llama import LlamaConfig, build_llama_stages, llama_loss_fn, llama_stage_costs
+    from elf_b200.models.llama import LlamaConfig, build_llama_stages, llama_loss_fn, llama_stage_costs, llama_stage_signatures
     from elf_b200.scheduling.schedulers import generate_zbv_schedule
 
     cfg = LlamaConfig(n_layers=5, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=256, seq_len=32, rope_theta=10000.0)
     placement = list(range(world)) + list(range(world - 1, -1, -1))
-    costs = llama_stage_costs(cfg, len(placement), placement, split_layers=True)
-    ref_stages = build_llama_stages(cfg, len(placement), dtype=torch.float32, seed=11, split_backward=False, placement=placement, split_layers=True)
+    costs = llama_stage_costs(cfg, len(placement), placement, split_layers=mode)
+    ref_stages = build_llama_stages(cfg, len(placement), dtype=torch.float32, seed=11, split_backward=False, placement=placement, split_layers=mode)
     kinds = {type(m).__name__ for s in ref_stages for m in s}
     assert {"LlamaAttentionBlock", "LlamaMLPBlock"} & kinds, kinds  # at least one layer is cut in two
+    signatures = llama_stage_signatures(cfg, len(placement), placement, mode)
+    if mode == "thirds":  # a boundary after the gate/up block carries the residual stream and the activation
+        assert "LlamaMLPUpBlock" in kinds and "LlamaMLPDownBlock" in kinds, kinds
+        assert any(sig.noutputs == 2 for sig in signatures) and any(sig.ninputs == 2 for sig in signatures)
     mine = [i for i, r in enumerate(placement) if r == rank]
-    stages = build_llama_stages(cfg, len(placement), only=mine, dtype=torch.float32, seed=11, placement=placement, split_layers=True)
+    stages = build_llama_stages(cfg, len(placement), only=mine, dtype=torch.float32, seed=11, placement=placement, split_layers=mode)
     g = torch.Generator().manual_seed(5)
     tok = torch.randint(0, cfg.vocab, (6, cfg.seq_len + 1), generator=g)
     ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
     sched = functools.partial(generate_zbv_schedule, cap="auto", stage_costs=costs, ratios=(1.0, 1.25, 0.9))
-    pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=sched, placement=placement, outputs="device")
+    pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=sched, placement=placement, outputs="device", signatures=signatures)
     _, loss = pipe(ids, tgt, llama_loss_fn, split_size=1)
     x = ids
     for s in ref_stages:
-        x = s(x)
+        x = s(*x) if isinstance(x, tuple) else s(x)
     ref_loss = llama_loss_fn(x, tgt)
     ref_loss.backward()
     if pipe.is_last():
@@ -219,5 +223,17 @@ def _split_layer_worker(rank, world):
     pipe.clear()
 
 
-def test_stages_cut_inside_layers():
-    run_ranks(_split_layer_worker, 2)
+@pytest.mark.parametrize("mode", [True, "thirds"])
+def test_stages_cut_inside_layers(mode):
+    run_ranks(_split_layer_worker, 2, mode)
+
+
+def test_thirds_cut_with_untagged_channels():
+    """Two tensors per boundary over one-communicator-per-channel p2p (NCCL-like matching)."""
+    import os
+
+    os.environ["ELF_B200_P2P_STRICT"] = "1"
+    try:
+        run_ranks(_split_layer_worker, 2, "thirds")
+    finally:
+        os.environ.pop("ELF_B200_P2P_STRICT")

@@ -120,6 +120,29 @@ def test_split_layer_modules_equal_whole_layer():
     torch.testing.assert_close(mlp(attn(x)), whole(x), atol=1e-5, rtol=1e-5)
 
 
+def test_mlp_up_down_blocks_equal_mlp_block():
+    import torch
+
+    from elf_b200.models.llama import LLAMA_CONFIGS, LlamaConfig, LlamaMLPBlock, LlamaMLPDownBlock, LlamaMLPUpBlock, _stage_ranges, init_llama_
+
+    cfg = LlamaConfig(n_layers=1, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=64, seq_len=16, rope_theta=10000.0)
+    whole = init_llama_(LlamaMLPBlock(cfg).float(), 0.1, seed=2)
+    up, down = LlamaMLPUpBlock(cfg).float(), LlamaMLPDownBlock(cfg).float()
+    up.load_state_dict({k: v for k, v in whole.state_dict().items() if k.split(".")[0] in ("norm2", "w_gate_up")})
+    down.load_state_dict({k: v for k, v in whole.state_dict().items() if k.split(".")[0] == "w_down"})
+    x = torch.randn(2, 16, 64)
+    torch.testing.assert_close(down(*up(x)), whole(x), atol=1e-5, rtol=1e-5)
+    # three cut points per layer bring the busiest rank of the 8B shape on 8 ranks within 2 % of the mean
+    placement = list(range(8)) + list(range(7, -1, -1))
+    for mode, bound in ((True, 1.11), ("thirds", 1.02)):
+        ranges, k, costs = _stage_ranges(LLAMA_CONFIGS["llama3-8b"], 16, placement, mode)
+        assert ranges[0][0] == 0 and ranges[-1][1] == k * 32 and all(a < b for a, b in ranges)
+        load = [0.0] * 8
+        for s, c in enumerate(costs):
+            load[placement[s]] += c
+        assert max(load) / (sum(load) / 8) < bound
+
+
 def test_zbv_auto_cap_is_never_worse_than_fixed_caps():
     from elf_b200.scheduling.scheduling import OperationType as T
     from elf_b200.scheduling.schedulers import generate_zbv_schedule
