@@ -202,9 +202,12 @@ class PipelineBlock:
         assert len(outputs) == len(out_grads)
         with self._timed(f"backward_inputs({self.id}:{mb_id})"):
             live = [(o, g) for o, g in zip(outputs, out_grads) if o.requires_grad]
-            for i, (o, g) in enumerate(live):
+            for o, g in live:
                 assert o.shape == g.shape, f"Output and grad shapes do not match: {o.shape} != {g.shape}"
-                torch.autograd.backward(o, g.to(o.dtype), retain_graph=i != len(live) - 1)
+            if live:
+                # one traversal for all outputs: shared nodes run their backward once (custom
+                # functions that free their state on the first call rely on this)
+                torch.autograd.backward([o for o, _ in live], [g.to(o.dtype) for o, g in live])
 
         in_grads = [x.grad.data if x.grad is not None else torch.zeros_like(x) for x in inputs if x.requires_grad]
 

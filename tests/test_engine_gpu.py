@@ -152,3 +152,38 @@ def test_timing_and_memory_statistics_on_gpu(dev):
     finally:
         os.environ.pop("ELF_TIMINGS")
         os.environ.pop("ELF_MEMORY")
+
+
+def test_two_tensor_stage_boundary_on_gpu(dev):
+    """Llama stages cut after a gate/up block: the boundary carries the residual stream and the
+    activation, the producing stage has two outputs whose gradients arrive together (one autograd
+    traversal, so the attention function's backward runs once).  Two stages on one GPU, ZB-V."""
+    from elf_b200 import Pipeline
+    from elf_b200.models.llama import LlamaConfig, build_llama_stages, llama_loss_fn, llama_stage_signatures
+    from elf_b200.ops import gemm as G
+
+    cfg = LlamaConfig(n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, ffn=512, vocab=512, seq_len=128, rope_theta=10000.0)
+    placement = [0, 0]
+    sigs = llama_stage_signatures(cfg, 2, placement, "thirds")
+    assert sigs[0].noutputs == 2 and sigs[1].ninputs == 2, "this shape is meant to be cut after a gate/up block"
+    stages = build_llama_stages(cfg, 2, device=dev, seed=5, placement=placement, split_layers="thirds")
+    ref = build_llama_stages(cfg, 2, device=dev, seed=5, placement=placement, split_layers="thirds", split_backward=False)
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g).to(dev)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    pipe = Pipeline(stages, None, partitioner=False, scheduler="zbv", placement=placement, outputs="none", signatures=sigs)
+    _, loss = pipe(ids, tgt, llama_loss_fn, split_size=1)
+    x = ids
+    for s in ref:
+        x = s(*x) if isinstance(x, tuple) else s(x)
+    ref_loss = llama_loss_fn(x, tgt)
+    ref_loss.backward()
+    torch.cuda.synchronize()
+    G.check_status(dev)
+    assert abs(loss.item() - ref_loss.item()) < 2e-2 * abs(ref_loss.item())
+    for block in pipe.blocks:
+        want = {n: p.grad for n, p in ref[block.id].named_parameters()}
+        for n, p in block.model.named_parameters():
+            key = n if n in want else n.replace(".layer.", ".")
+            err = ((p.grad.float() - want[key].float()).norm() / want[key].float().norm().clamp_min(1e-9)).item()
+            assert err < 5e-2, (block.id, n, err)
