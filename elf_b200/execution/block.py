@@ -263,9 +263,11 @@ class PipelineBlock:
         grads = [v[0].get(v[0].to_process, mb_id) for v in self.output_variables]
         with self._timed(f"recompute_backward_inputs({self.id}:{mb_id})"):
             live = [(o, g) for o, g in zip(outputs, grads) if o.requires_grad]
-            for i, (o, g) in enumerate(live):
-                # only the part of the backward that reaches the split-backward layers
-                partial_dx_recomputation(o, g.to(o.dtype), retain_graph=i != len(live) - 1)
+            # only the part of the backward that reaches the split-backward layers
+            if len(live) == 1:
+                partial_dx_recomputation(live[0][0], live[0][1].to(live[0][0].dtype))
+            elif live:
+                partial_dx_recomputation([o for o, _ in live], [g.to(o.dtype) for o, g in live])
         self._file_stashes("grad_output", mb_id)
 
     def _offload_dw(self, mb_id: int, to="cpu") -> None:

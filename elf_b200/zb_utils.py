@@ -404,6 +404,17 @@ def partial_dx_recomputation(outputs, grad_outputs=None, retain_graph: bool = Fa
     if grad_outputs is None:
         assert outputs.numel() == 1, "Implicit gradient outputs are only supported for scalar outputs"
         grad_outputs = torch.ones_like(outputs)
+    if isinstance(outputs, (list, tuple)):
+        # several outputs of one stage: one traversal, so that nodes they share run their backward once
+        seen, edges = set(), []
+        for o in outputs:
+            for e in _leaves_below_dx(o.grad_fn):
+                if e.node not in seen:
+                    seen.add(e.node)
+                    edges.append(e)
+        if edges:
+            torch.autograd.grad(list(outputs), inputs=edges, grad_outputs=list(grad_outputs), allow_unused=True, retain_graph=retain_graph)
+        return
     edges = _leaves_below_dx(outputs.grad_fn)
     if edges:
         torch.autograd.grad(outputs, inputs=edges, grad_outputs=grad_outputs, allow_unused=True, retain_graph=retain_graph)

@@ -256,3 +256,32 @@ def test_measured_stage_costs_needs_a_timed_step():
     pipe.zero_grad()
     _, loss = pipe(ids, tgt, GPT.loss_fn, split_size=1)
     assert torch.isfinite(loss)
+
+
+def test_remat_options_with_a_two_tensor_stage_boundary():
+    """Stages cut after a gate/up block (two outputs) under every rematerialisation option: the
+    recompute-backward differentiates both outputs in one traversal."""
+    from elf_b200.models.llama import LlamaConfig, build_llama_stages, llama_loss_fn, llama_stage_signatures
+
+    cfg = LlamaConfig(n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=512, seq_len=32, rope_theta=10000.0)
+    placement, nmb = [0, 0], 4
+    sigs = llama_stage_signatures(cfg, 2, placement, "thirds")
+    assert sigs[0].noutputs == 2
+    stages = build_llama_stages(cfg, 2, dtype=torch.float32, seed=5, placement=placement, split_layers="thirds")
+    ref = build_llama_stages(cfg, 2, dtype=torch.float32, seed=5, placement=placement, split_layers="thirds", split_backward=False)
+    sched = RematScheduler(SCHEDULERS["zbv"], fixed_solution(2, nmb, full_fwd=[(0, 1)], activations_bwd=[(0, 2), (1, 0)], full_bwd=[(0, 0), (1, 3)]))
+    pipe = Pipeline(stages, None, partitioner=False, scheduler=sched, placement=placement, outputs="none", signatures=sigs)
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    _, loss = pipe(ids, tgt, llama_loss_fn, split_size=1)
+    x = ids
+    for s in ref:
+        x = s(*x) if isinstance(x, tuple) else s(x)
+    ref_loss = llama_loss_fn(x, tgt)
+    ref_loss.backward()
+    torch.testing.assert_close(loss, ref_loss.detach(), atol=1e-4, rtol=1e-4)
+    for block in pipe.blocks:
+        want = {n: p.grad for n, p in ref[block.id].named_parameters()}
+        for n, p in block.model.named_parameters():
+            torch.testing.assert_close(p.grad, want[n if n in want else n.replace(".layer.", ".")], atol=1e-4, rtol=1e-3)
