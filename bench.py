@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
     ap.add_argument("--split-thirds", action="store_true", help="also allow a stage boundary after the MLP's SwiGLU (two tensors cross it); finer balance for deep pipelines")
+    ap.add_argument("--timeline", default=None, help="write every rank's per-operation device timeline of one extra step (JSON) to this file")
     ap.add_argument("--no-calibrate", action="store_true", help="keep the schedule laid out for the analytic stage costs (for comparison)")
     return ap.parse_args()
 
@@ -199,14 +200,19 @@ def run_ours(args):
                 per_stage.setdefault(int(m.group(2)), {}).setdefault(m.group(1), []).append(secs * 1e3)
         mine_ops = {s: [round(sum(v.get(k, [0.0])) / max(1, len(v.get(k, [0.0]))), 3) for k in ("forward", "backward_inputs", "backward_params")] for s, v in per_stage.items()}
         every = [None] * world
+        mine_tl = {"timeline": pipe.detailed_stats.get("timeline", {}), "host_enqueue": pipe.detailed_stats.get("host_enqueue", {}), "total_s": st.get("total")}
         if world > 1:
-            dist.all_gather_object(every, (mine_pct, mine_ops))
+            dist.all_gather_object(every, (mine_pct, mine_ops, mine_tl if args.timeline else None))
         else:
-            every = [(mine_pct, mine_ops)]
+            every = [(mine_pct, mine_ops, mine_tl if args.timeline else None)]
         op_ms = {}
-        for _, ops in every:
+        for _, ops, _tl in every:
             op_ms.update(ops)
-        every = [p for p, _ in every]
+        if args.timeline and rank == 0:
+            os.makedirs(os.path.dirname(os.path.abspath(args.timeline)), exist_ok=True)
+            with open(args.timeline, "w") as f:
+                json.dump({"placement": list(placement), "nmb": args.nmb, "pp": pp, "dp": dp, "ranks": {str(r): tl for r, (_, _, tl) in enumerate(every)}}, f)
+        every = [p for p, _, _tl in every]
         bubble = {
             "bubble_pct_mean": sum(every) / world,
             "bubble_pct_max": max(every),

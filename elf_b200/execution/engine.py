@@ -35,6 +35,7 @@ logger = logging.getLogger("engine")
 __all__ = ["Engine", "compute_loss", "preallocate_pool"]
 
 T = OperationType
+_COMPUTE_LIKE = (T.FORWARD, T.BACKWARD_INPUTS, T.BACKWARD_PARAMS, T.RECOMPUTE_FORWARD, T.RECOMPUTE_BACKWARD_INPUTS, T.LOSS_FORWARD, T.LOSS_BACKWARD)
 _GIB = 1 << 30
 _POOL_DTYPES = {
     "bf16": torch.bfloat16,
@@ -224,7 +225,10 @@ class Engine:
         ``stats``   ``total, idle, start_idle, end_idle, bubble`` in seconds; compute time
                     (hence idle/bubble) is measured only when ``ELF_TIMINGS`` is set
         ``detailed_stats``  ``all_events`` {timer name: s}, ``memories`` / ``peak_memory``
-                    {str(op): bytes} (peaks are per-op only when ``ELF_MEMORY`` is set)
+                    {str(op): bytes} (peaks are per-op only when ``ELF_MEMORY`` is set);
+                    with ``ELF_TIMINGS`` also ``timeline`` {timer name: (begin s, end s)} on the
+                    device clock, counted from the start of the step, and ``host_enqueue``
+                    {str(op): s} = when the host issued the operation
         """
         precise_timings = _env_flag("ELF_TIMINGS")
         precise_memory = _env_flag("ELF_MEMORY")
@@ -255,6 +259,7 @@ class Engine:
         warmup_time = None
         memories: "OrderedDict[str, int]" = OrderedDict()
         peaks: "OrderedDict[str, int]" = OrderedDict()
+        host_enqueue: Dict[str, float] = {}  # when the host issued each compute operation (ELF_TIMINGS only)
 
         for op in schedule:
             block = self.id_to_block.get(op.block_id)
@@ -273,6 +278,8 @@ class Engine:
             handler = self._handlers.get(op.op)
             if handler is None:
                 raise RuntimeError(f"Unknown operation : {op}")
+            if precise_timings and op.op in _COMPUTE_LIKE:
+                host_enqueue[str(op)] = time.perf_counter() - pipe_start
             handler(block, op)
             if self.on_cuda:
                 if precise_memory:
@@ -294,12 +301,19 @@ class Engine:
 
         compute_time = 0.0
         all_events: Dict[str, float] = {}
+        timeline: Dict[str, tuple] = {}
         if precise_timings:
             for block in self.blocks:
                 for timer in block.compute_time:
                     t = timer.time()
                     compute_time += t
                     all_events[timer.name] = t
+                    if self.on_cuda and hasattr(timer, "start_event"):
+                        # begin / end of the operation on the device, seconds after the step's start event
+                        t0 = ev_start.elapsed_time(timer.start_event) / 1e3
+                        timeline[timer.name] = (t0, t0 + t)
+                    elif hasattr(timer, "start"):
+                        timeline[timer.name] = (timer.start - pipe_start, timer.end - pipe_start)
         total = pipe_end - pipe_start
         stats = {
             "total": total,
@@ -308,7 +322,7 @@ class Engine:
             "end_idle": pipe_end - cooldown_start,
         }
         stats["bubble"] = stats["idle"] - stats["start_idle"] - stats["end_idle"]
-        detailed = {"all_events": all_events, "memories": memories, "peak_memory": peaks}
+        detailed = {"all_events": all_events, "memories": memories, "peak_memory": peaks, "timeline": timeline, "host_enqueue": host_enqueue}
         for block in self.blocks:
             block.compute_time.clear()
 
