@@ -479,15 +479,18 @@ const char* attention_backward(const AttnBwdArgs& a, cudaStream_t stream) {
   if (err) return err;
   err = make_tmap_out(&tdq, a.dq_acc, 2, tokens, q_cols, q_cols, 32, 128);  // fp32, 128-byte wide chunks
   if (err) return err;
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return "attention: cannot query the device";
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess) {
-      num_sms = 0;
+  // SM count and function attributes are per device
+  static int sms_of[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return "attention: cannot query the device";
+  if (sms_of[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return "attention: cannot query the device";
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
       return "attention: cannot raise the shared memory limit";
-    }
+    sms_of[dev] = n;
   }
+  const int num_sms = sms_of[dev];
   const float scale = a.scale > 0.f ? a.scale : 0.08838834764831845f;
   const long long rows = (long long)tokens * a.n_heads;
   attn_bwd_prepare<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dout), a.lse, a.lse2,

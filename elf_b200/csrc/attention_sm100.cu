@@ -465,15 +465,18 @@ const char* attention_forward(const AttnArgs& a, cudaStream_t stream) {
   CUtensorMap tq;
   const char* err = make_tmap_2d(&tq, a.qkv, 1, rows, pitch, pitch, 64, 128);
   if (err) return err;
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return "attention: cannot query the device";
-    if (cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess) {
-      num_sms = 0;
+  // SM count and function attributes are per device
+  static int sms_of[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return "attention: cannot query the device";
+  if (sms_of[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return "attention: cannot query the device";
+    if (cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess)
       return "attention: cannot raise the shared memory limit";
-    }
+    sms_of[dev] = n;
   }
+  const int num_sms = sms_of[dev];
   const float scale = a.scale > 0.f ? a.scale : 0.08838834764831845f;
   const int group = a.n_heads / a.n_kv_heads, n_q = a.seq / BQ;
   const long long items = group % 2 == 0 ? (long long)n_q * (a.n_heads / 2) * a.batch : (long long)((n_q + 1) / 2) * a.n_heads * a.batch;

@@ -48,6 +48,10 @@ __global__ void __launch_bounds__(256) finalize_reduce_kernel(uint4* __restrict_
     }
   }
   __syncthreads();
+  // A wait that ran out (here or in an earlier kernel of the step) means the inbox may hold
+  // stale or half-written data: leave the local gradient untouched.  The optimizer kernel
+  // reads the same status word and skips its update, and the host raises at the next step.
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != kOk) return;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 g = grad[i];
     float acc[8];

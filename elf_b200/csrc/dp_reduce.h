@@ -31,7 +31,7 @@ cudaError_t push_ranges(const void* grad, const long long* ranges_dev, int n_ran
 
 // Wait until the flags listed in wait_idx[0 .. n_wait) of every peer slot have reached
 // `flag_value` (flags only grow; each wait is bounded by `timeout_ns`; on a timeout `status`
-// gets kErrPeerTimeout and the reduction still runs on what is there), then
+// gets kErrPeerTimeout and the gradient is left as it was), then
 // grad[i] = scale * (grad[i] + sum_p inbox[p][i]) for i in [0, n).
 //   my_flags: n_peers * n_flags words in my own symmetric memory, peer-major.
 cudaError_t finalize_reduce(void* grad, const void* inbox, long long n, long long slot_stride, int n_peers, const int* my_flags,

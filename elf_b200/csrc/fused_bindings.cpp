@@ -148,8 +148,13 @@ void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dt
 }
 
 void adamw(at::Tensor& p, const at::Tensor& grad, at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double b1, double b2,
-           double eps, double wd, int64_t step, double grad_scale) {
+           double eps, double wd, int64_t step, double grad_scale, const c10::optional<at::Tensor>& status) {
   need_bf16(p, "param");
+  const int* status_ptr = nullptr;
+  if (status.has_value()) {
+    TORCH_CHECK(status->is_cuda() && status->scalar_type() == at::kInt && status->numel() >= 1, "status must be a CUDA int32 tensor");
+    status_ptr = status->data_ptr<int>();
+  }
   TORCH_CHECK(grad.is_contiguous() && grad.numel() == p.numel(), "grad must be contiguous and match param");
   TORCH_CHECK(grad.scalar_type() == at::kFloat || grad.scalar_type() == at::kBFloat16, "grad must be fp32 or bf16");
   for (const at::Tensor* t : {&master, &m, &v})
@@ -158,7 +163,7 @@ void adamw(at::Tensor& p, const at::Tensor& grad, at::Tensor& master, at::Tensor
   const double bc1 = 1.0 - std::pow(b1, (double)step), bc2 = 1.0 - std::pow(b2, (double)step);
   check(elfb::adamw_step(p.data_ptr(), grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr<float>(),
                          v.data_ptr<float>(), p.numel(), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1, (float)bc2,
-                         (float)grad_scale, cur()),
+                         (float)grad_scale, status_ptr, cur()),
         "adamw_step");
 }
 
@@ -185,6 +190,6 @@ void register_fused_ops(pybind11::module_& m) {
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw", &adamw, py::arg("param"), py::arg("grad"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("lr"),
-        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0);
+        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0, py::arg("status") = c10::nullopt);
   m.def("scale_", &scale_);
 }

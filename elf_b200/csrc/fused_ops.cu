@@ -392,9 +392,12 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat162* __restrict__ dout, co
 template <bool GRAD_F32>
 __global__ void adamw_kernel(Bf16x8* __restrict__ p, const void* __restrict__ grad, float* __restrict__ master,
                              float* __restrict__ m, float* __restrict__ v, long long n8, long long n, float lr, float b1,
-                             float b2, float eps, float decay, float inv_bc1, float inv_bc2, float gscale) {
+                             float b2, float eps, float decay, float inv_bc1, float inv_bc2, float gscale,
+                             const int* __restrict__ status) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
+  // a kernel of this step gave up on a bounded wait: the gradients cannot be trusted
+  if (status != nullptr && *status != 0) return;
   const long long base = i * 8;
   float g[8];
   if (base + 8 <= n) {
@@ -576,16 +579,16 @@ cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtabl
 
 cudaError_t adamw_step(void* p_bf16, const void* grad, bool grad_f32, float* master, float* m, float* v, long long n,
                        float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
-                       float grad_scale, cudaStream_t s) {
+                       float grad_scale, const int* status, cudaStream_t s) {
   if (n == 0) return cudaSuccess;
   const long long n8 = (n + 7) / 8;
   const float decay = 1.f - lr * weight_decay;
   if (grad_f32)
     adamw_kernel<true><<<blocks_for(n8, 256), 256, 0, s>>>((Bf16x8*)p_bf16, grad, master, m, v, n8, n, lr, beta1, beta2, eps,
-                                                           decay, 1.f / bc1, 1.f / bc2, grad_scale);
+                                                           decay, 1.f / bc1, 1.f / bc2, grad_scale, status);
   else
     adamw_kernel<false><<<blocks_for(n8, 256), 256, 0, s>>>((Bf16x8*)p_bf16, grad, master, m, v, n8, n, lr, beta1, beta2, eps,
-                                                            decay, 1.f / bc1, 1.f / bc2, grad_scale);
+                                                            decay, 1.f / bc1, 1.f / bc2, grad_scale, status);
   return cudaGetLastError();
 }
 

@@ -43,9 +43,12 @@ cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtabl
 // Fused AdamW over flat buffers: bf16 params, fp32 master/m/v, grads bf16 or fp32.
 //   g' = g * grad_scale; m = b1 m + (1-b1) g'; v = b2 v + (1-b2) g'^2
 //   master = master * (1 - lr*wd) - lr * (m / bc1) / (sqrt(v / bc2) + eps); p = bf16(master)
+// `status` (may be null): the per-device error record of this package's kernels; when its
+// first word is non-zero the update is skipped, so parameters never move on gradients that a
+// timed-out kernel left incomplete.
 cudaError_t adamw_step(void* p_bf16, const void* grad, bool grad_f32, float* master, float* m, float* v, long long n,
                        float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
-                       float grad_scale, cudaStream_t s);
+                       float grad_scale, const int* status, cudaStream_t s);
 
 // y = a * x (16-bit, in place allowed) — used for gradient scaling of flat buffers.
 cudaError_t scale_bf16(void* x, long long n, float a, cudaStream_t s);

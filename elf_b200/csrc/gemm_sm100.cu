@@ -357,11 +357,14 @@ template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tb4, void* d, const void* bias, int M, int N, int K,
                               long long ldd, uint32_t fmt, float alpha, int max_split, int* status, const PushTarget& push, int num_sms, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
-  static bool configured = false;
-  if (!configured) {
+  // function attributes are per device: remember which devices of this process have been set up
+  static bool configured[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;

@@ -440,11 +440,14 @@ template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool BIAS>
 static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& g, int num_sms, cudaStream_t stream) {
   using namespace pair;
   auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, OUT_F32, ACCUM, BIAS>;
-  static bool configured = false;
-  if (!configured) {
+  // function attributes are per device: remember which devices of this process have been set up
+  static bool configured[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
   const int tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
   int pairs = num_sms / 2;

@@ -12,6 +12,9 @@
 
 namespace elfb {
 
+// Host-side per-device caches (function attributes, SM counts) are indexed by device ordinal.
+constexpr int kMaxDevices = 64;
+
 // ----------------------------------------------------------------------------------------
 // Error words written by kernels into a caller-provided int[4] status buffer.
 //   status[0] = error code (0 = ok), status[1] = role/where, status[2..3] = detail

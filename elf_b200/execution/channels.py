@@ -46,6 +46,13 @@ def edge_list(signatures) -> List[Tuple[int, int]]:
     return sorted(edges)
 
 
+def _done(work) -> bool:
+    try:
+        return work.is_completed()
+    except Exception:
+        return True
+
+
 class _Pending:
     __slots__ = ("work", "tensor", "mb")
 
@@ -146,6 +153,13 @@ class Channel:
         pending = self._posted.pop(mb)
         pending.work.wait()
         return pending.tensor
+
+    def abandon(self) -> None:
+        """Forget posted receives and send handles without waiting for the peer (used when
+        a step is given up after an error; the peer may be gone)."""
+        self._sends = [(w, t) for w, t in self._sends if not _done(w)]
+        self._posted.clear()
+        self._deferred.clear()
 
     def reset(self) -> None:
         self.reap_sends(block=True)

@@ -32,6 +32,8 @@ __all__ = [
     "matmul_nt",
     "status",
     "check_status",
+    "snapshot_status_async",
+    "raise_if_failed",
     "set_enabled",
     "set_variant",
 ]
@@ -59,7 +61,10 @@ def set_variant(variant: int, split_tail: bool = True) -> None:
 
 def status(device=None) -> torch.Tensor:
     """Per-device int32[4] error record the kernels write on a bounded-wait timeout."""
-    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if isinstance(device, int):
+        idx = device
+    else:
+        idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
     if idx not in _STATUS:
         _STATUS[idx] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
     return _STATUS[idx]
@@ -70,8 +75,51 @@ def check_status(device=None) -> None:
     rec = status(device).tolist()
     if rec[0] != 0:
         status(device).zero_()
-        what = {1: "an mbarrier wait timed out", 2: "a wait on a peer GPU timed out", 3: "bad shape"}.get(rec[0], "unknown")
+        what = _WHAT.get(rec[0], "unknown")
         raise RuntimeError(f"elf_b200 kernel error {rec[0]} ({what}); detail={rec[1:]}")
+
+
+_SNAPSHOT: Dict[int, tuple] = {}  # device index -> (pinned int32[4], event of the last copy into it)
+_WHAT = {1: "an mbarrier wait timed out", 2: "a wait on a peer GPU timed out", 3: "bad shape"}
+
+
+def snapshot_status_async(device=None) -> None:
+    """Queue a copy of the device's error record into pinned host memory on the current
+    stream (16 bytes, no synchronisation).  ``raise_if_failed`` later looks at the copy."""
+    if not torch.cuda.is_available():
+        return
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if idx not in _STATUS:
+        return  # no kernel of this package has been given a status word on this device yet
+    entry = _SNAPSHOT.get(idx)
+    if entry is None:
+        entry = _SNAPSHOT[idx] = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+    host, event = entry
+    with torch.cuda.device(idx):
+        host.copy_(_STATUS[idx], non_blocking=True)
+        event.record()
+
+
+def raise_if_failed(device=None) -> None:
+    """Non-blocking check of the last completed ``snapshot_status_async``: raises when a
+    kernel of an earlier step recorded an error (a bounded wait that ran out).  Called at the
+    start of ``Pipeline.step`` and ``FusedAdamW.step``; after an error the optimizer kernel
+    has skipped its update, so parameters are still those of the last good step."""
+    if not _SNAPSHOT:
+        return
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    entry = _SNAPSHOT.get(idx)
+    if entry is None:
+        return
+    host, event = entry
+    if not event.query():
+        return  # the copy has not landed yet; the next call will see it
+    rec = host.tolist()
+    if rec[0] != 0:
+        host.zero_()
+        status(idx).zero_()
+        raise RuntimeError(f"elf_b200 kernel error {rec[0]} ({_WHAT.get(rec[0], 'unknown')}) in an earlier step; detail={rec[1:]}. "
+                           "The optimizer skipped the update of that step; gradients of that step are not valid.")
 
 
 def usable(x: torch.Tensor, w: torch.Tensor) -> bool:

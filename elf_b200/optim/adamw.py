@@ -13,6 +13,7 @@ On CPU tensors, or for dtypes other than bf16, the same class drives plain torch
 from __future__ import annotations
 
 import math
+import weakref
 from typing import Iterable, List, Optional
 
 import torch
@@ -51,6 +52,19 @@ class FusedAdamW:
             self.exp_avg.append(torch.zeros(g.numel, dtype=torch.float32, device=g.device))
             self.exp_avg_sq.append(torch.zeros(g.numel, dtype=torch.float32, device=g.device))
         self.param_groups = [{"params": [p for g in self.groups for p in g.params], "lr": lr}]
+        for g in self.groups:  # lets whoever rewrites the parameters (a checkpoint load) find the fp32 copies
+            g.optimizers = [o for o in getattr(g, "optimizers", []) if o() is not None] + [weakref.ref(self)]
+
+    def resync_master(self) -> None:
+        """Re-derive the fp32 master weights from the current parameter values.  Needed after
+        anything other than this optimizer wrote the parameters (``load_state_dict`` on the
+        model, ``Pipeline.load_checkpoint``): ``step`` rewrites the parameters from the master
+        copy, so a stale master would silently undo the load.  ``Pipeline.load_checkpoint``
+        calls this for every optimizer built over its parameters."""
+        with torch.no_grad():
+            for g, w in zip(self.groups, self.master):
+                if w.data_ptr() != g.flat_param.data_ptr():
+                    w.copy_(g.flat_param)
 
     def _kernel_ok(self, g: FlatGroup) -> bool:
         if g.device.type != "cuda" or g.dtype != torch.bfloat16:
@@ -66,13 +80,21 @@ class FusedAdamW:
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0) -> None:
+        if self.groups and self.groups[0].device.type == "cuda":
+            from ..ops import gemm
+
+            gemm.raise_if_failed(self.groups[0].device)
         self.step_count += 1
         b1, b2 = self.betas
         lr = self.param_groups[0].get("lr", self.lr)
         for g, w, m, v in zip(self.groups, self.master, self.exp_avg, self.exp_avg_sq):
             g.gather_stray_grads()
             if self._kernel_ok(g):
-                _ext.get().adamw(g.flat_param, g.flat_grad, w, m, v, lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale)
+                from ..ops import gemm
+
+                _ext.get().adamw(g.flat_param, g.flat_grad, w, m, v, lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale,
+                                 gemm.status(g.device))
+                gemm.snapshot_status_async(g.device)
                 continue
             grad = g.flat_grad.float() * grad_scale
             m.mul_(b1).add_(grad, alpha=1 - b1)

@@ -41,6 +41,7 @@ from .execution.engine import Engine
 from .partitioners.signature import Signature, sequential_signatures
 from .registry import COMM_SCHEDULERS, PARTITIONERS, SCHEDULERS, TRACERS, resolve
 from .scheduling import add_comms, check_schedule_validity, schedule_to_str
+from .scheduling.scheduling import OperationType
 from .utils.metadata import TensorMetadata
 from .utils.placement import Placement
 from .utils.shipping import broadcast_models, recv_models, send_models, transport_device
@@ -284,6 +285,10 @@ class Pipeline:
         replicas — and ``(None, None)`` elsewhere.  Gradients are left in ``p.grad``,
         scaled for the mean loss and averaged over replicas; they accumulate across calls
         until ``zero_grad``."""
+        if self.device.type == "cuda":
+            from .ops import gemm as _gemm
+
+            _gemm.raise_if_failed(self.device)  # a bounded device wait that ran out in an earlier step
         if batch is not None and isinstance(batch, torch.Tensor):
             batch = [batch]
         mb_sizes = self._get_mb_sizes(split_size, batch)
@@ -296,14 +301,24 @@ class Pipeline:
         for block in self.blocks:
             for layer in block.dw_layers():
                 layer.clear()
-        if self.grad_sync is not None:
+        if self.grad_sync is not None and any(op.op is OperationType.ALL_REDUCE_PARAM_GRADS for op in self.schedule):
+            # only a step that exchanges gradients opens a new exchange epoch (and flips the inbox
+            # parity): an inference step in between must not let the next training step write
+            # into the half of the inbox a slower replica may still be reading
             self.grad_sync.begin_step()
 
         if batch is not None:
             batch = [t.to(self.device, non_blocking=True) if t.device != self.device else t for t in batch]
         if target is not None and target.device != self.device:
             target = target.to(self.device, non_blocking=True)
-        result, losses, stats, detailed = self.engine.train_step(batch, target, loss_fn, self.schedule, mb_sizes, profile)
+        try:
+            result, losses, stats, detailed = self.engine.train_step(batch, target, loss_fn, self.schedule, mb_sizes, profile)
+        except BaseException:
+            # an operation raised (user loss function, a peer that went away, ...): drop every
+            # half-finished micro-batch so that the pipeline object stays usable - a later step,
+            # ``clear()`` and checkpointing must not trip over stale slots or pending receives
+            self._abandon_step()
+            raise
 
         for block in self.blocks:
             block._wait_for_send_ops()
@@ -312,6 +327,8 @@ class Pipeline:
             for ch in self.channels.channels.values():
                 ch._posted.clear()
         self.stats, self.detailed_stats = stats, detailed
+        if self.device.type == "cuda":
+            _gemm.snapshot_status_async(self.device)
 
         if self.blocks and self.blocks[-1].is_last and (losses or result):
             loss = None
@@ -329,6 +346,28 @@ class Pipeline:
         return None, None
 
     __call__ = step
+
+    def _abandon_step(self) -> None:
+        """Forget the state of a step that did not finish: slots, W-pass stashes, offloaded
+        activations, posted receives and send handles (without waiting for peers)."""
+        for block in self.blocks:
+            try:
+                block.clear_slots()
+                block.compute_time.clear()
+                block._pending_reduce.clear()
+            except Exception:  # pragma: no cover - best effort while another error propagates
+                logger.exception("while abandoning a step on %s", block)
+        if self.channels is not None:
+            for ch in self.channels.channels.values():
+                ch.abandon()
+        eng = self.engine
+        try:
+            eng.offload.finish_step(getattr(eng, "_offloaders", {}).values())
+        except Exception:  # pragma: no cover
+            logger.exception("while releasing offloaded activations")
+        eng._offloaders = {}
+        eng._results, eng._grad_fns, eng._losses = {}, {}, {}
+        eng._microbatches = eng._targets = None
 
     def _get_mb_sizes(self, split_size, batch) -> List[int]:
         """``0`` → ``batch // pp`` per micro-batch; an int → equal chunks plus a remainder;
@@ -473,12 +512,40 @@ class Pipeline:
     def load_checkpoint(self, epoch="init", dir_path="./", strict: bool = True) -> dict:
         """Restore this rank's stages from a ``checkpoint`` file; returns the whole
         dictionary so callers can pick up their ``extra`` entries."""
-        state = torch.load(self._ckpt_path(epoch, dir_path), map_location=self.device, weights_only=False)
+        path = self._ckpt_path(epoch, dir_path)
+        if not os.path.isfile(path):
+            raise FileNotFoundError(f"no checkpoint for dp={self.dp_rank}, pp={self.pp_rank} at {path}")
+        try:
+            state = torch.load(path, map_location=self.device, weights_only=False)
+        except Exception as exc:
+            raise RuntimeError(f"checkpoint {path} cannot be read (truncated or corrupt file?): {type(exc).__name__}: {exc}") from exc
+        if not isinstance(state, dict):
+            raise RuntimeError(f"checkpoint {path} does not hold a checkpoint dictionary (got {type(state).__name__})")
+        held = sorted(int(k[len("state_dict_"):]) for k in state if isinstance(k, str) and k.startswith("state_dict_") and k[len("state_dict_"):].isdigit())
         for block in self.blocks:
             key = f"state_dict_{block.id}"
             if key not in state:
-                raise KeyError(f"checkpoint has no entry for stage {block.id}")
-            block.model.load_state_dict(state[key], strict=strict)
+                raise RuntimeError(
+                    f"checkpoint {path} has no entry for stage {block.id}: it holds stages {held} "
+                    f"(written by pp rank {state.get('pp')}, dp rank {state.get('dp')}); was it saved with another placement?"
+                )
+        for block in self.blocks:
+            try:
+                block.model.load_state_dict(state[f"state_dict_{block.id}"], strict=strict)
+            except RuntimeError as exc:
+                raise RuntimeError(f"checkpoint {path}: stage {block.id} does not match this pipeline's stage: {exc}") from exc
+        # optimizers with fp32 master weights over these parameters must follow the load, or
+        # their next step would write the old weights back
+        seen = set()
+        for p in self.parameters():
+            group = getattr(p, "_elf_flat_group", None)
+            if group is None or id(group) in seen:
+                continue
+            seen.add(id(group))
+            for ref in getattr(group, "optimizers", []):
+                opt = ref()
+                if opt is not None:
+                    opt.resync_master()
         return state
 
     def gather_parameters(self, dst: int = 0) -> dict:

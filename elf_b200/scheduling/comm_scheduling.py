@@ -169,7 +169,9 @@ def add_comms(schedule: List[Operation], signatures: List[Signature]) -> List[Op
             peers = _ordered(sig.get_all_targets(), False) if fwd else _ordered(sig.get_all_sources(), True)
             extra += [Operation(op.block_id, op.mb_id, send_t, op.rank, dst=p) for p in peers]
     schedule.extend(extra)
-    if (T.ALL_REDUCE_PARAM_GRADS) not in {op.op for op in schedule}:
+    kinds = {op.op for op in schedule}
+    # a schedule without any backward (inference) produces no gradients: nothing to exchange
+    if T.ALL_REDUCE_PARAM_GRADS not in kinds and kinds & {T.BACKWARD_INPUTS, T.BACKWARD_PARAMS}:
         for stage, rank in dict.fromkeys((op.block_id, op.rank) for op in schedule):
             schedule.append(Operation(stage, None, T.ALL_REDUCE_PARAM_GRADS, rank))
     return schedule

@@ -226,7 +226,7 @@ def test_stats_and_inference():
         ids, tgt = data()
         pipe(ids, tgt, GPT.loss_fn, split_size=2)
         assert set(pipe.stats) == {"total", "idle", "start_idle", "end_idle", "bubble"}
-        assert set(pipe.detailed_stats) == {"all_events", "memories", "peak_memory"}
+        assert {"all_events", "memories", "peak_memory"} <= set(pipe.detailed_stats)
         names = set(pipe.detailed_stats["all_events"])
         assert {"forward(0:0)", "backward_inputs(0:1)", "backward_params(0:0)", "loss_forward", "backward(0:0)"} <= names
         assert pipe.stats["idle"] <= pipe.stats["total"]
