@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
     ap.add_argument("--split-thirds", action="store_true", help="also allow a stage boundary after the MLP's SwiGLU (two tensors cross it); finer balance for deep pipelines")
     ap.add_argument("--timeline", default=None, help="write every rank's per-operation device timeline of one extra step (JSON) to this file")
+    ap.add_argument("--p2p", choices=["auto", "nccl", "copy"], default="auto", help="stage-to-stage transport: NCCL send/recv kernels, or copy-engine writes into the consumer's ring buffer")
     ap.add_argument("--no-calibrate", action="store_true", help="keep the schedule laid out for the analytic stage costs (for comparison)")
     return ap.parse_args()
 
@@ -94,7 +95,7 @@ def run_ours(args):
 
         scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
         sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
-    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", signatures=signatures)
+    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", signatures=signatures, p2p=args.p2p)
     params = list(pipe.parameters())
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()
 
@@ -251,6 +252,7 @@ def run_ours(args):
             "placement": list(placement),
             "layers_per_stage": counts,
             "optimizer": "fused AdamW, fp32 master/m/v, step inside the timed region",
+            "p2p": (pipe.channels.transport if pipe.channels is not None else "none"),
             "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed",
         },
         "clocks": clocks.summary(),

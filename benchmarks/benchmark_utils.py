@@ -19,6 +19,12 @@ import torch.distributed as dist
 from elf_b200.scheduling.scheduling import Operation, OperationType, OpOptions, compute_types
 
 __all__ = [
+    "bench",
+    "meta_to_device",
+    "balanced_partition",
+    "get_handcrafted_partition",
+    "get_handcrafted_imbalanced_partition",
+    "check_correctness",
     "init_dist",
     "ClockSampler",
     "max_over_ranks",
@@ -185,3 +191,220 @@ def get_offloaded_scheduler(scheduler, ratio: int, prefetching_time: int = 1) ->
     from elf_b200.scheduling.offload_sched import offload_every
 
     return offload_every(scheduler, ratio, prefetching_time)
+
+
+# ---------------------------------------------------------------------------------------
+# timing harness, hand-made partitions, pipeline-vs-single-process check
+# ---------------------------------------------------------------------------------------
+
+
+def meta_to_device(model: torch.nn.Module, device="cuda", std: float = 0.02, seed: Optional[int] = None) -> torch.nn.Module:
+    """Materialise a module built under ``torch.device("meta")`` on ``device`` and initialise
+    it: modules that define ``reset_parameters`` use it, remaining matrices get N(0, ``std``),
+    remaining vectors their customary constant (1 for norm gains, 0 for biases).  The
+    reference's helper of the same name (``benchmarks/benchmark_utils.py:146-152``) looks for
+    ``reset_parameters`` on *parameters* and therefore leaves memory uninitialised."""
+    if any(p.is_meta for p in model.parameters()) or any(b.is_meta for b in model.buffers()):
+        model.to_empty(device=device)
+    else:
+        model.to(device)
+    gen = torch.Generator(device="cpu")
+    if seed is not None:
+        gen.manual_seed(seed)
+    done = set()
+    for module in model.modules():
+        reset = getattr(module, "reset_parameters", None)
+        if callable(reset):
+            reset()
+            done.update(id(p) for p in module.parameters(recurse=False))
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if id(p) in done:
+                continue
+            if p.dim() >= 2:
+                p.copy_(torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=gen))
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.fill_(1.0)
+    return model
+
+
+def balanced_partition(n: int, placement: List[int]) -> List[int]:
+    """Blocks per stage for ``n`` equal blocks: the remainder goes to the middle stages first
+    (from the back), then to the first stage; the last stage, which also carries the head, is
+    served last (``benchmarks/benchmark_utils.py:155-172`` of the reference)."""
+    k = len(placement)
+    counts = [n // k] * k
+    order = [k - i for i in range(2, k + 1)] + [k - 1]
+    for i in order[: n % k]:
+        counts[i] += 1
+    return counts
+
+
+def get_handcrafted_imbalanced_partition(model, rank: int, placement: List[int], factors: List[int], device=None) -> List[torch.nn.Module]:
+    """Stages hosted by pipeline rank ``rank`` when stage ``i`` takes ``factors[i]`` consecutive
+    entries of ``model.blocks``; ``model.embed`` joins the first stage, ``model.ln`` / ``model.head``
+    the last.  The stages are materialised on ``device`` (default: this process's GPU, else CPU)."""
+    blocks = list(model.blocks)
+    assert sum(factors) == len(blocks), f"factors {factors} do not cover the {len(blocks)} blocks"
+    assert len(factors) == len(placement)
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    stages, start = [], 0
+    for i, n in enumerate(factors):
+        mods = blocks[start : start + n]
+        start += n
+        if i == 0:
+            mods = [m for m in (getattr(model, "embed", None),) if m is not None] + mods
+        if i == len(factors) - 1:
+            mods += [m for m in (getattr(model, "ln", None), getattr(model, "head", None)) if m is not None]
+        stages.append(torch.nn.Sequential(*mods))
+    mine = [s for s, r in zip(stages, placement) if r == rank]
+    return [meta_to_device(s, device) for s in mine]
+
+
+def get_handcrafted_partition(model, rank: int, placement: List[int], device=None) -> List[torch.nn.Module]:
+    return get_handcrafted_imbalanced_partition(model, rank, placement, balanced_partition(len(model.blocks), placement), device)
+
+
+def bench(model, parts, scheduler, placement, dtype=torch.float32, nmb: Optional[int] = None, ntrials: int = 1, stats_file: Optional[str] = None,
+          n_iterations: int = 16, warmup: int = 3, optimizer_factory: Optional[Callable] = None, **pipeline_kwargs):
+    """Time a pre-partitioned pipeline the way the reference's harness does
+    (``benchmarks/benchmark_utils.py:69-143``): micro-batch size 1, ``nmb = 2 * world`` unless
+    given, ``warmup`` untimed steps, then ``ntrials`` trials of ``n_iterations`` steps; returns
+    ``(median seconds per iteration, peak GB of every rank (rank 0 only), all trial times)``.
+    On GPUs a trial is timed with CUDA events and the maximum over ranks is taken; on CPU by
+    wall clock.  ``optimizer_factory(params)`` adds an optimizer step to every iteration."""
+    from elf_b200 import Pipeline, sequential_signatures
+
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    n_micro_batches = nmb or 2 * world
+    batch = n_micro_batches  # micro-batch size 1
+    pipe = Pipeline(parts, None, placement=list(placement), partitioner=False, scheduler=scheduler, signatures=sequential_signatures(placement), **pipeline_kwargs)
+    device = pipe.device
+    on_cuda = device.type == "cuda"
+    opt = optimizer_factory(list(pipe.parameters())) if optimizer_factory is not None else None
+
+    def one_step():
+        if opt is not None:
+            opt.zero_grad()
+        else:
+            pipe.zero_grad(set_to_none=False)
+        pipe(model.get_sample(batch, dtype, device), model.get_target(batch, dtype, device), model.loss_fn, split_size=1)
+        if opt is not None:
+            opt.step()
+
+    for _ in range(warmup):
+        one_step()
+    if on_cuda:
+        torch.cuda.reset_peak_memory_stats(device)
+    times = []
+    for _ in range(ntrials):
+        if on_cuda:
+            torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        if on_cuda:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+        for _ in range(n_iterations):
+            one_step()
+        if on_cuda:
+            b.record()
+            torch.cuda.synchronize(device)
+            secs = max_over_ranks(a.elapsed_time(b) / 1e3, device)
+        else:
+            if world > 1:
+                dist.barrier()
+            secs = time.perf_counter() - t0
+        times.append(secs / n_iterations)
+    peak = torch.cuda.max_memory_allocated(device) / 2**30 if on_cuda else 0.0
+    peaks = None
+    if world > 1:
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object(peak, gathered, dst=0)
+        peaks = gathered
+    elif rank == 0:
+        peaks = [peak]
+    if stats_file is not None:
+        write_detailed_stats(stats_file, pipe.detailed_stats, rank, world)
+    pipe.clear()
+    return statistics.median(times), peaks, times
+
+
+def check_correctness(model, pipe, atol: float = 1e-3, rtol: float = 1e-3, batch: Optional[int] = None) -> Dict[str, float]:
+    """Compare one pipeline step with the same model run in a single process.
+
+    The single-process copy is rebuilt on the rank that owns the last stage from
+    ``pipe.gather_parameters`` (so it holds exactly the pipeline's weights), run on the same
+    inputs, and outputs, loss and every parameter gradient are compared with
+    ``atol`` / ``rtol`` (the reference's check, ``benchmarks/benchmark_utils.py:215-292``,
+    uses 1e-3 for both).  ``model`` must be the un-partitioned module whose parameter names
+    the stages kept (fx partitions do; hand-made ``nn.Sequential`` stages of ``model.blocks``
+    do not).  The pipeline must have been built with ``outputs="cpu"`` or ``"device"``.
+    Returns the largest absolute differences seen; raises ``AssertionError`` on a mismatch."""
+    import copy
+
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    device = pipe.device
+    n = batch or 2 * max(1, pipe.pp)
+    inputs = model.get_sample(n, device=device) if rank == 0 else None
+    targets = model.get_target(n, device=device) if rank == 0 else None
+    if world > 1:
+        box = [inputs.cpu() if inputs is not None else None, targets.cpu() if targets is not None else None]
+        dist.broadcast_object_list(box, src=0)
+        inputs, targets = box[0].to(device), box[1].to(device)
+    was_training = [b.model.training for b in pipe.blocks]
+    for b in pipe.blocks:
+        b.model.eval()  # no dropout on either side
+    pipe.zero_grad()
+    outputs, loss = pipe(inputs, targets, model.loss_fn, split_size=1)
+    grads = {name: p.grad.detach().float().cpu() for name, p in pipe.named_parameters() if p.grad is not None}
+    owner = (pipe.dp_rank * pipe.pp) + pipe.placement[-1]
+    params = pipe.gather_parameters(dst=owner)
+    report: Dict[str, float] = {}
+    if world > 1:
+        all_grads = [None] * world if rank == owner else None
+        dist.gather_object(grads, all_grads, dst=owner)
+    else:
+        all_grads = [grads]
+    if rank == owner:
+        ref = copy.deepcopy(model)
+        if any(p.is_meta for p in ref.parameters()):
+            ref.to_empty(device="cpu")
+        ref = ref.to("cpu").float()
+        missing = ref.load_state_dict({k: v.detach().float().cpu() for k, v in params.items()}, strict=False)
+        assert not missing.missing_keys, f"parameters the pipeline does not hold: {missing.missing_keys[:5]}"
+        ref.eval()
+        y_ref = ref(inputs.cpu())
+        loss_ref = model.loss_fn(y_ref, targets.cpu())
+        loss_ref.backward()
+        for module in ref.modules():  # split-backward layers: run the deferred weight-gradient pass
+            if hasattr(module, "move_last_computed") and hasattr(module, "backward") and hasattr(module, "ctx"):
+                module.move_last_computed("input", 0)
+                module.move_last_computed("grad_output", 0)
+                module.backward(0)
+        y = torch.cat([o.detach().float().cpu() for o in outputs]) if outputs else None
+        if y is not None:
+            report["output"] = float((y - y_ref.detach()).abs().max())
+            torch.testing.assert_close(y, y_ref.detach(), atol=atol, rtol=rtol, msg=lambda m: f"pipeline output differs from the single-process model: {m}")
+        report["loss"] = float((loss.detach().float().cpu() - loss_ref.detach()).abs())
+        torch.testing.assert_close(loss.detach().float().cpu(), loss_ref.detach(), atol=atol, rtol=rtol, msg=lambda m: f"loss differs: {m}")
+        ref_grads = {k: p.grad for k, p in ref.named_parameters() if p.grad is not None}
+        worst = 0.0
+        for part in all_grads:
+            for name, g in part.items():
+                assert name in ref_grads, f"gradient for {name} has no counterpart in the single-process model"
+                worst = max(worst, float((g - ref_grads[name]).abs().max()))
+                torch.testing.assert_close(g, ref_grads[name], atol=atol, rtol=rtol, msg=lambda m, name=name: f"gradient of {name} differs: {m}")
+        report["grad"] = worst
+    for b, t in zip(pipe.blocks, was_training):
+        b.model.train(t)
+    pipe.zero_grad()
+    if world > 1:
+        dist.barrier()
+    return report

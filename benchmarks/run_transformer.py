@@ -73,6 +73,8 @@ def parse_args():
     ap.add_argument("--memory-budget", type=int, help="MB per GPU; enables ILP rematerialisation")
     ap.add_argument("--tracer", default="default", choices=TRACERS.available() if len(TRACERS) else ["default"])
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "symm"])
+    ap.add_argument("--p2p", default="auto", choices=["auto", "nccl", "copy"], help="stage-to-stage transport")
+    ap.add_argument("--offload-ilp", action="store_true", help="with --memory-budget: let the ILP also offload activations to pinned host memory")
     return ap.parse_args()
 
 
@@ -156,7 +158,8 @@ def main():
     if budget is not None and not args.no_optimizer:
         budget -= n_params * torch.empty(0, dtype=dtype).element_size() / world / 2**20
     config = PipelineConfig(partitioner=partitioner, scheduler=scheduler, placement=list(placement), tracer=args.tracer, pp=pp, dp=args.dp,
-                            memory_budget=budget, signatures=signatures, outputs="none", grad_sync=args.grad_sync)
+                            memory_budget=budget, signatures=signatures, outputs="none", grad_sync=args.grad_sync, p2p=args.p2p,
+                            offload=args.offload_ilp)
     pipe = Pipeline(parts, sample, config=config)
     if world > 1:
         dist.barrier()

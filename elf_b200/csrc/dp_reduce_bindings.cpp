@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "dp_reduce.h"
+#include "p2p_signal.h"
 
 namespace {
 
@@ -40,9 +41,26 @@ void finalize_reduce(at::Tensor& grad, const at::Tensor& inbox, int64_t n_peers,
         "finalize_reduce");
 }
 
+// flag addresses arrive as integers: they may point into a peer's symmetric memory
+void p2p_signal(int64_t flag_addr, int64_t value) {
+  TORCH_CHECK(flag_addr != 0 && flag_addr % 4 == 0, "bad flag address");
+  check(elfb::p2p_signal(reinterpret_cast<int*>(flag_addr), (int)value, at::cuda::getCurrentCUDAStream()), "p2p_signal");
+}
+
+void p2p_wait(const at::Tensor& flags, int64_t index, int64_t value, double timeout_ms, const c10::optional<at::Tensor>& status, int64_t where) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() && index >= 0 && index < flags.numel(), "flags must be an int32 CUDA tensor holding `index`");
+  c10::cuda::CUDAGuard g(flags.device());
+  int* st = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+  check(elfb::p2p_wait(flags.data_ptr<int>() + index, (int)value, (unsigned long long)(timeout_ms * 1e6), st, (int)where, at::cuda::getCurrentCUDAStream()),
+        "p2p_wait");
+}
+
 }  // namespace
 
 void register_dp_reduce(pybind11::module_& m) {
   m.def("push_ranges", &push_ranges, "copy ranges of my gradient buffer into my slot on every peer and flag them");
   m.def("finalize_reduce", &finalize_reduce, "wait for the peers' flags, then grad = scale * (grad + sum of inbox slots)");
+  m.def("p2p_signal", &p2p_signal, "after the current stream's prior work: store `value` (release, system scope) to the flag at `flag_addr`");
+  m.def("p2p_wait", &p2p_wait, "block the current stream until flags[index] >= value (bounded by timeout_ms; records a peer timeout in `status`)",
+        py::arg("flags"), py::arg("index"), py::arg("value"), py::arg("timeout_ms"), py::arg("status") = c10::nullopt, py::arg("where") = 0);
 }

@@ -147,6 +147,20 @@ void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dt
         "embedding_backward");
 }
 
+void embedding_bwd_sorted(const at::Tensor& dout, const at::Tensor& sorted_ids, const at::Tensor& perm, at::Tensor& grad) {
+  need_bf16(dout, "dout");
+  TORCH_CHECK(dout.is_contiguous(), "dout must be contiguous");
+  TORCH_CHECK(grad.is_cuda() && grad.is_contiguous() && grad.dim() == 2 && (grad.scalar_type() == at::kFloat || grad.scalar_type() == at::kBFloat16),
+              "grad must be a contiguous [vocab, dim] fp32 or bf16 CUDA tensor");
+  for (const at::Tensor* t : {&sorted_ids, &perm})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() && t->dim() == 1, "sorted_ids / perm must be 1-D contiguous int64 CUDA");
+  TORCH_CHECK(sorted_ids.numel() == perm.numel() && dout.numel() == perm.numel() * grad.size(1), "shape mismatch between dout, ids and grad");
+  c10::cuda::CUDAGuard g(dout.device());
+  check(elfb::embedding_backward_sorted(dout.data_ptr(), sorted_ids.data_ptr<int64_t>(), perm.data_ptr<int64_t>(), grad.data_ptr(),
+                                        grad.scalar_type() == at::kFloat, (int)perm.numel(), (int)grad.size(1), (long long)grad.size(0), cur()),
+        "embedding_backward_sorted");
+}
+
 void adamw(at::Tensor& p, const at::Tensor& grad, at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double b1, double b2,
            double eps, double wd, int64_t step, double grad_scale, const c10::optional<at::Tensor>& status) {
   need_bf16(p, "param");
@@ -189,6 +203,7 @@ void register_fused_ops(pybind11::module_& m) {
         py::arg("scale") = 1.0, py::arg("ignore_index") = -100);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_bwd_sorted", &embedding_bwd_sorted);
   m.def("adamw", &adamw, py::arg("param"), py::arg("grad"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("lr"),
         py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0, py::arg("status") = c10::nullopt);
   m.def("scale_", &scale_);

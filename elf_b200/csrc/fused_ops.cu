@@ -388,6 +388,46 @@ __global__ void embedding_bwd_kernel(const __nv_bfloat162* __restrict__ dout, co
   }
 }
 
+// Deterministic embedding backward: `sorted_ids` are the token ids in ascending order and
+// `perm[k]` the row of `dout` that sorted position k came from (a stable sort).  Block k owns
+// the run of equal ids that starts at position k (blocks in the middle of a run exit), sums the
+// rows of that run in order in fp32 and adds the sum to the token's row of `grad` - straight
+// into the parameter's gradient buffer, no dense temporary, no atomics.
+template <bool GRAD_F32>
+__global__ void __launch_bounds__(256) embedding_bwd_sorted_kernel(const Bf16x8* __restrict__ dout, const int64_t* __restrict__ sorted_ids,
+                                                                   const int64_t* __restrict__ perm, void* __restrict__ grad, int rows,
+                                                                   int dim8, long long vocab) {
+  const int k = blockIdx.x;
+  const int64_t token = sorted_ids[k];
+  if (k > 0 && sorted_ids[k - 1] == token) return;  // not the head of its run
+  if (token < 0 || token >= vocab) return;          // padding / ignored ids carry no gradient
+  int len = 1;
+  while (k + len < rows && sorted_ids[k + len] == token) ++len;
+  for (int c = threadIdx.x; c < dim8; c += blockDim.x) {
+    float acc[8];
+    if (GRAD_F32) {
+      const float4* g = reinterpret_cast<const float4*>(grad) + ((long long)token * dim8 + c) * 2;
+      const float4 a = g[0], b = g[1];
+      acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+    } else {
+      unpack8(reinterpret_cast<const Bf16x8*>(grad)[(long long)token * dim8 + c], acc);
+    }
+    for (int j = 0; j < len; ++j) {
+      float v[8];
+      unpack8(dout[(long long)perm[k + j] * dim8 + c], v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    if (GRAD_F32) {
+      float4* g = reinterpret_cast<float4*>(grad) + ((long long)token * dim8 + c) * 2;
+      g[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      g[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      reinterpret_cast<Bf16x8*>(grad)[(long long)token * dim8 + c] = pack8(acc);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ AdamW
 template <bool GRAD_F32>
 __global__ void adamw_kernel(Bf16x8* __restrict__ p, const void* __restrict__ grad, float* __restrict__ master,
@@ -574,6 +614,17 @@ cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtabl
     embedding_bwd_kernel<true><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
   else
     embedding_bwd_kernel<false><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_backward_sorted(const void* dout, const int64_t* sorted_ids, const int64_t* perm, void* grad, bool grad_f32, int rows,
+                                      int dim, long long vocab, cudaStream_t s) {
+  if (dim % 8) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  if (grad_f32)
+    embedding_bwd_sorted_kernel<true><<<rows, 256, 0, s>>>((const Bf16x8*)dout, sorted_ids, perm, grad, rows, dim / 8, vocab);
+  else
+    embedding_bwd_sorted_kernel<false><<<rows, 256, 0, s>>>((const Bf16x8*)dout, sorted_ids, perm, grad, rows, dim / 8, vocab);
   return cudaGetLastError();
 }
 

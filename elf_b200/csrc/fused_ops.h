@@ -37,6 +37,11 @@ cudaError_t cross_entropy_backward(const void* logits, void* dlogits, const int6
 // out[row] = table[ids[row]]
 cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s);
 // dtable[ids[row]] += dout[row]   (fp32 or bf16 table gradient; atomics)
+// grad[sorted_ids[k]] += dout[perm[k]] for every k, deterministically: equal ids are adjacent in
+// `sorted_ids` (ascending, stable), one CTA sums a run in order and adds it to the gradient row
+// (bf16 or fp32) in place.  Ids outside [0, vocab) are skipped.
+cudaError_t embedding_backward_sorted(const void* dout, const int64_t* sorted_ids, const int64_t* perm, void* grad, bool grad_f32, int rows,
+                                      int dim, long long vocab, cudaStream_t s);
 cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim,
                                cudaStream_t s);
 

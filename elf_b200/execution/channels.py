@@ -11,6 +11,15 @@ always agree on ordering.  Transport:
   signatures, which every rank already knows, so no ``all_gather_object`` round is needed
   and each group is created exactly once.
 * gloo (CPU): the pipeline group with a per-(channel, micro-batch) tag.
+* copy (GPUs of one node, ``ChannelTable.upgrade_to_copy``): after a first step over NCCL has
+  told both ends the message size, a channel can switch to a ring of receive slots in the
+  consumer's memory (symmetric memory mapped by the producer).  The producer writes a slot with
+  the copy engines on a side stream and raises a sequence number; the consumer's compute stream
+  waits for it (bounded), copies the slot out and acknowledges it.  No SM-resident kernel
+  competes with the persistent GEMMs, which NCCL's send/recv kernels do: next to a
+  weight-gradient-sized GEMM a 32 MiB NCCL message in each direction costs the GEMM about as
+  long as the message itself takes, the same copy through the copy engines about 5 %
+  (``benchmarks/p2p_overlap.py``).
 
 Shape/dtype are learned by the receiving end from a one-off int64 header message that
 precedes the first payload (the reference sends 16 floats with a blocking ``recv``,
@@ -83,6 +92,8 @@ class Channel:
         # ELF_B200_P2P_STRICT=1 makes gloo behave like NCCL (untagged, one group per channel)
         # so that ordering or size mismatches show up in CPU tests.
         self._tagged = dist.get_backend(group) != "nccl" and os.environ.get("ELF_B200_P2P_STRICT", "0") != "1"
+        self.max_message_bytes = 0  # largest payload seen so far (sent or posted), sizes the copy transport's slots
+        self.link: Optional["_CopyLink"] = None  # set by switch_to_copy
 
     def _tag(self, mb: int, header: bool = False) -> int:
         if not self._tagged:
@@ -95,6 +106,10 @@ class Channel:
         if payload.device != self.device:
             payload = payload.to(self.device)
         payload = payload.contiguous()
+        self.max_message_bytes = max(self.max_message_bytes, payload.numel() * payload.element_size())
+        if self.link is not None:
+            self.link.send(payload)
+            return
         if not self.header_sent:
             self.header_sent = True
             head = TensorMetadata(shape=list(payload.shape[1:]), dtype=payload.dtype).to_tensor(self.device)
@@ -130,6 +145,13 @@ class Channel:
         self._post(mb, batch)
 
     def _post(self, mb: int, batch: int) -> None:
+        nbytes = batch * self.metadata.dtype.itemsize
+        for d in self.metadata.shape:
+            nbytes *= d
+        self.max_message_bytes = max(self.max_message_bytes, nbytes)
+        if self.link is not None:
+            self._posted[mb] = _Pending(mb, None, self.link.post((batch, *self.metadata.shape), self.metadata.dtype))
+            return
         buf = torch.empty((batch, *self.metadata.shape), dtype=self.metadata.dtype, device=self.device)
         work = dist.irecv(buf, src=self.peer, group=self.group, tag=self._tag(mb))
         self._posted[mb] = _Pending(mb, work, buf)
@@ -151,6 +173,8 @@ class Channel:
                 raise KeyError(f"no recv posted for micro-batch {mb} on channel {self}")
             self._resolve_header()
         pending = self._posted.pop(mb)
+        if pending.work is None:  # copy transport: `tensor` holds the ticket of the posted receive
+            return self.link.take(pending.tensor)
         pending.work.wait()
         return pending.tensor
 
@@ -158,8 +182,33 @@ class Channel:
         """Forget posted receives and send handles without waiting for the peer (used when
         a step is given up after an error; the peer may be gone)."""
         self._sends = [(w, t) for w, t in self._sends if not _done(w)]
+        if self.link is not None and self._posted:
+            # receives that were posted but never taken leave the two ends' sequence numbers
+            # out of step: the ring cannot be trusted any more
+            self.link.broken = True
         self._posted.clear()
         self._deferred.clear()
+
+    def switch_to_copy(self, depth: int = 4, timeout_ms: float = 60000.0) -> bool:
+        """Collective over the two ranks of this channel: agree on the slot size (the largest
+        message either end has seen), allocate and map the ring, and route all later traffic
+        through it.  Returns whether the channel switched (it stays on NCCL if it has carried
+        no message yet).  Call between steps, with nothing of this channel in flight."""
+        assert not self._posted and not self._deferred, "switch_to_copy with receives in flight"
+        self.reap_sends(block=True)
+        size = torch.tensor([self.max_message_bytes], dtype=torch.int64, device=self.device)
+        dist.all_reduce(size, op=dist.ReduceOp.MAX, group=self.group)
+        slot_bytes = int(size.item())
+        if slot_bytes == 0:
+            return False
+        self.link = _CopyLink(self, (slot_bytes + 255) // 256 * 256, depth, timeout_ms)
+        return True
+
+    def end_step(self) -> None:
+        """Forget receives that were posted but not consumed in the step that just ended."""
+        if self._posted and self.link is not None:
+            self.link.broken = True
+        self._posted.clear()
 
     def reset(self) -> None:
         self.reap_sends(block=True)
@@ -168,6 +217,93 @@ class Channel:
 
     def __repr__(self) -> str:
         return f"Channel({self.src_block}->{self.dst_block} {self.direction}, peer={self.peer})"
+
+
+class _CopyLink:
+    """One end of a channel on the copy transport.
+
+    Both ranks allocate the same symmetric buffer: ``depth`` slots of ``slot_bytes`` followed by
+    a flag area.  The consumer's copy holds the ring; flag 0 of the consumer = sequence number
+    of the newest message that has landed, flag 1 of the producer = newest message the consumer
+    has copied out (so slot reuse never overtakes the consumer).  Messages are numbered 1, 2, ...
+    for the life of the channel and must be taken in the order they were posted, which is the
+    order they are sent in (the same rule NCCL imposes)."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, channel: "Channel", slot_bytes: int, depth: int, timeout_ms: float):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from ..ops import _ext
+        from ..ops import gemm as _gemm
+
+        _ext.require_on_gpu()
+        self.ext = _ext.get()
+        if not hasattr(self.ext, "p2p_signal"):
+            raise RuntimeError("extension built without the p2p flag kernels")
+        self.channel = channel
+        self.device = channel.device
+        self.depth, self.slot_bytes, self.timeout_ms = depth, slot_bytes, timeout_ms
+        total = depth * slot_bytes + self.FLAG_BYTES
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buf, group=channel.group.group_name)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=channel.group)  # nobody raises a flag before both rings are zeroed
+        me = self.handle.rank
+        peer = 1 - me
+        self.flags = self.buf[depth * slot_bytes :].view(torch.int32)
+        self.peer_buf = self.handle.get_buffer(peer, (total,), torch.uint8)
+        self.peer_flag_addr = int(self.handle.buffer_ptrs[peer]) + depth * slot_bytes
+        self.status = _gemm.status(self.device)
+        self.stream = torch.cuda.Stream(self.device)  # producer side: copies run here, behind the compute stream's event
+        self.sent = 0  # producer: messages sent
+        self.posted = 0  # consumer: receives posted
+        self.taken = 0  # consumer: receives taken
+        self.where = 100 + channel.index
+        self.broken = False
+
+    def _check(self) -> None:
+        if self.broken:
+            raise RuntimeError(f"{self.channel}: a step was abandoned with receives in flight; the copy transport of this channel is out of step with its peer - rebuild the pipeline")
+
+    # producer ---------------------------------------------------------------------------
+    def send(self, payload: torch.Tensor) -> None:
+        self._check()
+        nbytes = payload.numel() * payload.element_size()
+        if nbytes > self.slot_bytes:
+            raise RuntimeError(f"{self.channel}: message of {nbytes} bytes exceeds the ring's slot size {self.slot_bytes} (sized from the first step)")
+        self.sent += 1
+        seq = self.sent
+        slot = (seq - 1) % self.depth
+        cur = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(cur)  # the payload's producer kernels
+        with torch.cuda.stream(self.stream):
+            if seq > self.depth:  # the consumer must have copied out the message this one overwrites
+                self.ext.p2p_wait(self.flags, 1, seq - self.depth, self.timeout_ms, self.status, self.where)
+            self.peer_buf[slot * self.slot_bytes : slot * self.slot_bytes + nbytes].copy_(payload.reshape(-1).view(torch.uint8), non_blocking=True)
+            self.ext.p2p_signal(self.peer_flag_addr, seq)
+        payload.record_stream(self.stream)
+
+    # consumer ---------------------------------------------------------------------------
+    def post(self, shape, dtype):
+        self._check()
+        self.posted += 1
+        return (self.posted, tuple(shape), dtype)
+
+    def take(self, ticket) -> torch.Tensor:
+        self._check()
+        seq, shape, dtype = ticket
+        if seq != self.taken + 1:
+            raise RuntimeError(f"{self.channel}: receives must be consumed in the order they were posted (next is {self.taken + 1}, asked for {seq})")
+        self.taken = seq
+        slot = (seq - 1) % self.depth
+        out = torch.empty(shape, dtype=dtype, device=self.device)
+        nbytes = out.numel() * out.element_size()
+        self.ext.p2p_wait(self.flags, 0, seq, self.timeout_ms, self.status, self.where)
+        out.reshape(-1).view(torch.uint8).copy_(self.buf[slot * self.slot_bytes : slot * self.slot_bytes + nbytes], non_blocking=True)
+        self.ext.p2p_signal(self.peer_flag_addr + 4, seq)  # flag 1 of the producer: slot may be reused
+        return out
 
 
 class ChannelTable:
@@ -191,6 +327,8 @@ class ChannelTable:
                 width = max(1, sum(1 for src in signatures[b].sources if src == a))
                 edges += [(a, b, k) for k in range(width)]
         n = 2 * len(edges)
+        self._order: List[Tuple[int, int, str, int]] = []  # this rank's channels in creation order (the same relative order on both ends)
+        self.transport = "nccl" if backend == "nccl" else backend
         for replica in range(dp if dedicated_groups else 1):
             if not dedicated_groups:
                 replica = dp_rank
@@ -210,10 +348,27 @@ class ChannelTable:
                     src, dst = (a, b) if direction == "fwd" else (b, a)
                     peer_local = rb if local_rank == ra else ra
                     self.channels[(src, dst, direction, k)] = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
+                    self._order.append((src, dst, direction, k))
 
     def get(self, src_block: int, dst_block: int, direction: str, k: int = 0) -> Channel:
         """Channel of the ``k``-th tensor that ``src_block`` sends to ``dst_block``."""
         return self.channels[(src_block, dst_block, direction, k)]
+
+    def upgrade_to_copy(self, depth: int = 4, timeout_ms: float = 60000.0) -> int:
+        """Switch every channel that has carried traffic to the copy transport.  Every rank of
+        the job calls this at the same point between two steps; channels are visited in their
+        global creation order, and each switch only involves the channel's two ranks, so ranks
+        that share several channels meet them in the same order.  Returns how many of this rank's
+        channels switched."""
+        if self.transport != "nccl" or not self._groups:
+            raise RuntimeError("the copy transport needs CUDA tensors and one NCCL group per channel")
+        switched = 0
+        for key in self._order:
+            ch = self.channels[key]
+            if ch.link is None and ch.switch_to_copy(depth, timeout_ms):
+                switched += 1
+        self.transport = "copy"
+        return switched
 
     def reset(self) -> None:
         for ch in self.channels.values():

@@ -271,9 +271,7 @@ class Engine:
                 torch.cuda.reset_peak_memory_stats(self.device)
             if warmup_time is None and op.op is not T.RECV_FORWARD:
                 warmup_time = 0.0
-                if precise_timings:
-                    if self.on_cuda:
-                        torch.cuda.synchronize(self.device)
+                if precise_timings and not self.on_cuda:
                     warmup_time = time.perf_counter() - pipe_start
             handler = self._handlers.get(op.op)
             if handler is None:
@@ -308,12 +306,20 @@ class Engine:
                     t = timer.time()
                     compute_time += t
                     all_events[timer.name] = t
+                    key, k = timer.name, 0
+                    while key in timeline:  # timers that share a name (loss_forward): keep them all
+                        k += 1
+                        key = f"{timer.name}#{k}"
                     if self.on_cuda and hasattr(timer, "start_event"):
                         # begin / end of the operation on the device, seconds after the step's start event
                         t0 = ev_start.elapsed_time(timer.start_event) / 1e3
-                        timeline[timer.name] = (t0, t0 + t)
+                        timeline[key] = (t0, t0 + t)
                     elif hasattr(timer, "start"):
-                        timeline[timer.name] = (timer.start - pipe_start, timer.end - pipe_start)
+                        timeline[key] = (timer.start - pipe_start, timer.end - pipe_start)
+        if precise_timings and self.on_cuda and timeline:
+            # time until the first operation starts on the device, read from the events: a device
+            # synchronisation here would also wait for receives posted ahead of their use
+            warmup_time = max(0.0, min(t0 for t0, _ in timeline.values()))
         total = pipe_end - pipe_start
         stats = {
             "total": total,

@@ -97,7 +97,8 @@ class LlamaEmbedding(nn.Module):
         self.weight = nn.Parameter(torch.empty(cfg.vocab, cfg.d_model))
 
     def forward(self, ids):
-        return _f.embedding(self.weight, ids)
+        # the weight gradient is summed per token straight into the (flat) gradient buffer
+        return _f.embedding(self.weight, ids, into_grad=True)
 
 
 class LlamaDecoderLayer(nn.Module):

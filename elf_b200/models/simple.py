@@ -121,21 +121,32 @@ class TransformerBlock(nn.Module):
         return x + self.drop(self.fc2(F.gelu(self.fc1(self.ln2(x)))))
 
 
+class TokenEmbedding(nn.Module):
+    """Token embedding plus learned positions: one module, so that a hand-made first stage
+    (``nn.Sequential(model.embed, *blocks)``) computes what the whole model computes."""
+
+    def __init__(self, vocab: int, hidden_dim: int, seq_len: int):
+        super().__init__()
+        self.tok = nn.Embedding(vocab, hidden_dim)
+        self.pos = nn.Embedding(seq_len, hidden_dim)
+
+    def forward(self, ids):
+        return self.tok(ids) + self.pos(torch.arange(ids.size(1), device=ids.device))[None]
+
+
 class FullTransformer(nn.Module):
     """Embedding + pre-LN GELU blocks + LM head; cross-entropy in fp32."""
 
     def __init__(self, input_dim: int = 1024, hidden_dim: int = 256, n_blocks: int = 4, seq_len: int = 128, num_heads: int = 4, ffn_dim: Optional[int] = None, dropout: float = 0.0, causal: bool = True, **_unused):
         super().__init__()
         self.vocab, self.seq_len = input_dim, seq_len
-        self.embed = nn.Embedding(input_dim, hidden_dim)
-        self.pos = nn.Embedding(seq_len, hidden_dim)
+        self.embed = TokenEmbedding(input_dim, hidden_dim, seq_len)
         self.blocks = nn.Sequential(*[TransformerBlock(hidden_dim, num_heads, ffn_dim or 4 * hidden_dim, dropout, causal) for _ in range(n_blocks)])
         self.ln = nn.LayerNorm(hidden_dim)
         self.head = nn.Linear(hidden_dim, input_dim, bias=False)
 
     def forward(self, ids):
-        pos = torch.arange(ids.size(1), device=ids.device)
-        return self.head(self.ln(self.blocks(self.embed(ids) + self.pos(pos)[None])))
+        return self.head(self.ln(self.blocks(self.embed(ids))))
 
     def get_sample(self, batch_size, dtype=None, device="cpu"):
         return torch.randint(0, self.vocab, (batch_size, self.seq_len), device=device)

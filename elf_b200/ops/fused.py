@@ -203,21 +203,40 @@ def cross_entropy(logits: torch.Tensor, target: torch.Tensor, reduction: str = "
 
 # ------------------------------------------------------------------------------ embedding
 class _Embedding(torch.autograd.Function):
+    """Gather forward; the backward sorts the token ids (4 k integers) and sums the output
+    gradient rows of each token in order - deterministic, no atomics.  With ``into_grad`` the sums
+    are added straight into ``table.grad`` (or ``table.main_grad``), which is how the pipeline
+    runs it: no dense ``[vocab, dim]`` temporary per micro-batch."""
+
     @staticmethod
-    def forward(ctx, table, ids):
+    def forward(ctx, table, ids, into_grad):
         ctx.save_for_backward(ids)
+        ctx.table = table if into_grad else None
         ctx.shape = table.shape
         return _ext.get().embedding_fwd(table, ids.contiguous())
 
     @staticmethod
     def backward(ctx, dout):
         (ids,) = ctx.saved_tensors
-        dtable = torch.zeros(ctx.shape, dtype=torch.float32, device=dout.device)
-        _ext.get().embedding_bwd(dout.contiguous(), ids.contiguous(), dtable)
-        return dtable.to(dout.dtype), None
+        sorted_ids, perm = torch.sort(ids.reshape(-1), stable=True)
+        table = ctx.table
+        if table is not None:
+            target = getattr(table, "main_grad", None)
+            if target is None:
+                if table.grad is None:
+                    table.grad = torch.zeros_like(table)
+                target = table.grad
+            if target.is_contiguous() and target.dtype in (torch.bfloat16, torch.float32):
+                _ext.get().embedding_bwd_sorted(dout.contiguous(), sorted_ids, perm, target)
+                return None, None, None
+        dtable = torch.zeros(ctx.shape, dtype=dout.dtype, device=dout.device)
+        _ext.get().embedding_bwd_sorted(dout.contiguous(), sorted_ids, perm, dtable)
+        return dtable, None, None
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+def embedding(table: torch.Tensor, ids: torch.Tensor, into_grad: bool = False) -> torch.Tensor:
+    """``table[ids]``.  ``into_grad=True`` (for parameters): the backward accumulates into
+    ``table.grad`` in place instead of handing autograd a dense gradient."""
     if kernels_apply(table) and table.shape[1] % 8 == 0 and table.is_contiguous():
-        return _Embedding.apply(table, ids)
+        return _Embedding.apply(table, ids, bool(into_grad) and table.requires_grad and table.is_leaf)
     return F.embedding(ids, table)

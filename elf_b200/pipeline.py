@@ -19,8 +19,9 @@ Deliberate differences:
   on CPU/gloo;
 * ``load_checkpoint`` restores what ``checkpoint`` wrote; ``save`` works for every rank;
 * ``scheduler="auto"`` without a memory budget means 1F1B instead of failing later;
-* extra options: ``outputs`` ("cpu" as the reference, "device", or "none") and
-  ``grad_sync`` ("auto" | "nccl" | "symm").
+* extra options: ``outputs`` ("cpu" as the reference, "device", or "none"),
+  ``grad_sync`` ("auto" | "nccl" | "symm"), ``offload`` (the ILP may offload activations) and
+  ``p2p`` ("auto" | "nccl" | "copy": transport between stages).
 """
 
 from __future__ import annotations
@@ -64,6 +65,7 @@ class PipelineConfig:
     pp, dp          pipeline / data parallel sizes (``pp`` defaults to ``world // dp``)
     worker          rank that traces, partitions and solves the ILP
     memory_budget   per-GPU budget in **MB**; enables ILP rematerialisation
+    offload         with a memory budget: let the ILP also park activations in pinned host memory
     signatures      stage signatures of a pre-partitioned model
     """
 
@@ -79,6 +81,8 @@ class PipelineConfig:
     signatures: Optional[List[Signature]] = None
     outputs: str = "cpu"
     grad_sync: str = "auto"
+    offload: bool = False
+    p2p: str = "auto"
 
     def resolve(self) -> "PipelineConfig":
         """Copy with registry keys replaced by the registered callables (``False`` stays)."""
@@ -148,6 +152,7 @@ class Pipeline:
         self.engine = Engine(self.blocks, outputs=self.cfg.outputs)
         self._configure_grad_sync()
 
+        self._transport_decided = False
         self.schedule: list = []
         self.full_schedule: list = []
         self.last_nmb = 0
@@ -161,9 +166,9 @@ class Pipeline:
             assert sample is not None, "sample is required when memory_budget is set (used for profiling)"
             self._remat_stats = profile_all_stages(self.blocks, self.signatures, self.placement, sample, self.pp_group)
             if self._scheduler_name == "auto":
-                self.scheduler = AutoScheduler(self._remat_stats, self.cfg.memory_budget, self.cfg.worker, group=self.pp_group)
+                self.scheduler = AutoScheduler(self._remat_stats, self.cfg.memory_budget, self.cfg.worker, group=self.pp_group, offload=bool(self.cfg.offload))
             else:
-                self.scheduler = stagerematify(self.scheduler, self._remat_stats, self.cfg.memory_budget, self.cfg.worker, group=self.pp_group)
+                self.scheduler = stagerematify(self.scheduler, self._remat_stats, self.cfg.memory_budget, self.cfg.worker, group=self.pp_group, offload=bool(self.cfg.offload))
 
     # ------------------------------------------------------------------ set-up
     def _to_global(self, pp_local_rank: int) -> int:
@@ -325,7 +330,8 @@ class Pipeline:
             block.clear_slots()
         if self.channels is not None:
             for ch in self.channels.channels.values():
-                ch._posted.clear()
+                ch.end_step()
+            self._maybe_switch_transport()
         self.stats, self.detailed_stats = stats, detailed
         if self.device.type == "cuda":
             _gemm.snapshot_status_async(self.device)
@@ -346,6 +352,23 @@ class Pipeline:
         return None, None
 
     __call__ = step
+
+    def _maybe_switch_transport(self) -> None:
+        """After the first completed step (which told every channel its message size over NCCL),
+        move stage-to-stage traffic to the copy-engine transport when ``p2p="copy"`` asks for it
+        (``"auto"`` follows the ``ELF_B200_P2P`` environment variable, default NCCL)."""
+        if self._transport_decided:
+            return
+        self._transport_decided = True
+        want = self.cfg.p2p if self.cfg.p2p != "auto" else os.environ.get("ELF_B200_P2P", "nccl")
+        if want != "copy":
+            return
+        if self.device.type != "cuda" or self.channels.transport != "nccl":
+            logger.warning("p2p='copy' needs CUDA devices and NCCL process groups; staying on %s", self.channels.transport)
+            return
+        timeout_ms = 1e3 * self._timeout.total_seconds() if self._timeout is not None else 60000.0
+        n = self.channels.upgrade_to_copy(timeout_ms=timeout_ms)
+        logger.info("rank %d: %d channel(s) now use the copy-engine transport", self.rank, n)
 
     def _abandon_step(self) -> None:
         """Forget the state of a step that did not finish: slots, W-pass stashes, offloaded

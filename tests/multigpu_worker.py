@@ -7,6 +7,8 @@ Cases
               of the NCCL all-reduce path and of a single-process reference
   pp          pp=N, dp=1 ZB-V: loss and gradients equal the single-process reference
   pp_dp       pp=N/2, dp=2 1F1B with the peer-memory exchange
+  pp_copy     pp=N ZB-V with stage-to-stage traffic on the copy-engine transport from the second
+              step on (three steps; loss and gradients equal the single-process reference)
 """
 
 import os
@@ -59,6 +61,8 @@ def run(case):
         cfg = LlamaConfig(n_layers=5, d_model=256, n_heads=4, n_kv_heads=2, ffn=512, vocab=1024, seq_len=128, rope_theta=10000.0)
     elif case == "pp_dp":
         pp, dp, sched, modes = world // 2, 2, "1f1b", ["symm"]
+    elif case == "pp_copy":
+        pp, dp, sched, modes = world, 1, "zbv", ["nccl"]
     else:
         raise SystemExit(f"unknown case {case}")
     placement = Placement.default(sched, pp)
@@ -81,11 +85,12 @@ def run(case):
     results = {}
     for mode in modes:
         stages = build_llama_stages(cfg, n_stages, only=mine, device=dev, seed=7, **cut)
-        pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", grad_sync=mode)
+        pipe = Pipeline([stages[i] for i in mine], None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", grad_sync=mode,
+                        p2p="copy" if case == "pp_copy" else "nccl")
         if mode == "symm":
             assert pipe.grad_sync is not None, "peer-memory gradient exchange was not set up"
         tok = tokens[dp_rank * per_replica : (dp_rank + 1) * per_replica]
-        for _ in range(2):  # second step exercises the other inbox parity
+        for _ in range(3 if case == "pp_copy" else 2):  # second step exercises the other inbox parity (and the copy transport)
             pipe.zero_grad(set_to_none=False)
             _, loss = pipe(tok[:, :-1].contiguous(), tok[:, 1:].contiguous(), llama_loss_fn, split_size=per_replica // nmb)
         torch.cuda.synchronize()
@@ -99,6 +104,10 @@ def run(case):
                 worst = max(worst, e)
                 assert e < 6e-2, (mode, block.id, n, e)
         results[mode] = worst
+        if case == "pp_copy":
+            links = [ch.link for ch in pipe.channels.channels.values()]
+            assert links and all(l is not None for l in links), "channels did not switch to the copy transport"
+            assert any(l.sent > 0 for l in links) and any(l.taken > 0 for l in links)
         if mode == "symm":
             assert all(len(ex.pushed) > 0 for ex in pipe.grad_sync.exchanges.values() if ex is not None), "no gradient left through a GEMM epilogue"
         pipe.clear()

@@ -1,0 +1,62 @@
+"""The benchmark harness pieces: hand-made partitions, meta-device materialisation, the timing
+loop and the pipeline-vs-single-process check (CPU, one process and gloo ranks)."""
+
+import pytest
+import torch
+
+from benchmarks.benchmark_utils import balanced_partition, bench, check_correctness, get_handcrafted_partition, meta_to_device
+from elf_b200 import Pipeline, replace_layer_with_layer_dw
+from elf_b200.models.simple import FullTransformer
+from tests.dist_utils import run_ranks
+
+SMALL = dict(input_dim=64, hidden_dim=32, n_blocks=5, seq_len=16, num_heads=2, ffn_dim=64)
+
+
+def test_balanced_partition_puts_the_remainder_in_the_middle_first():
+    assert balanced_partition(8, [0, 1, 2, 3]) == [2, 2, 2, 2]
+    assert balanced_partition(9, [0, 1, 2, 3]) == [2, 2, 3, 2]
+    assert balanced_partition(10, [0, 1, 2, 3]) == [2, 3, 3, 2]
+    assert balanced_partition(11, [0, 1, 2, 3]) == [3, 3, 3, 2]
+    assert sum(balanced_partition(30, list(range(8)))) == 30
+
+
+def test_meta_to_device_initialises_everything():
+    with torch.device("meta"):
+        model = FullTransformer(**SMALL)
+    assert all(p.is_meta for p in model.parameters())
+    meta_to_device(model, "cpu", seed=0)
+    for name, p in model.named_parameters():
+        assert not p.is_meta and torch.isfinite(p).all(), name
+    assert float(model.head.weight.detach().std()) > 0
+    out = model(model.get_sample(2))
+    assert out.shape == (2, SMALL["seq_len"], SMALL["input_dim"])
+
+
+def test_handcrafted_partition_and_bench_loop():
+    with torch.device("meta"):
+        model = FullTransformer(**SMALL)
+    placement = [0, 0, 0]
+    parts = get_handcrafted_partition(model, 0, placement, device="cpu")
+    assert [sum(1 for m in p if type(m).__name__ == "TransformerBlock") for p in parts] == [2, 2, 1]
+    assert isinstance(parts[0][0], torch.nn.Module) and parts[-1][-1] is model.head
+    for p in parts:
+        replace_layer_with_layer_dw(p)
+    median, peaks, times = bench(model, parts, "afab", placement, nmb=2, ntrials=2, n_iterations=2, warmup=1, outputs="none")
+    assert len(times) == 2 and median > 0 and peaks == [0.0]
+
+
+def _correctness_worker(rank, world):
+    torch.manual_seed(0)
+    model = FullTransformer(**SMALL)
+    replace_layer_with_layer_dw(model)
+    sample = model.get_sample(1)
+    pipe = Pipeline(model, sample, scheduler="1f1b", partitioner="constrained", outputs="device")
+    report = check_correctness(model, pipe)
+    if rank == pipe.placement[-1]:
+        assert set(report) == {"output", "loss", "grad"} and report["grad"] < 1e-3
+    pipe.clear()
+
+
+@pytest.mark.dist
+def test_check_correctness_two_ranks():
+    run_ranks(_correctness_worker, 2)

@@ -33,6 +33,10 @@ def test_pipeline_stages_cut_inside_layers_two_gpus():
     launch("pp_split", 2)
 
 
+def test_pipeline_copy_engine_transport_two_gpus():
+    launch("pp_copy", 2)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_pipeline_with_replicas_four_gpus():
     launch("pp_dp", 4)

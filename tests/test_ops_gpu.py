@@ -199,6 +199,37 @@ def test_embedding(dev):
     assert rel_err(table.grad, tf.grad) < 1e-2
 
 
+def test_embedding_backward_into_the_gradient_buffer(dev):
+    """Many repeated tokens, two micro-batches accumulating into one bf16 and one fp32 gradient
+    buffer, against an fp32 index_add; the result must also be bit-identical from run to run."""
+    from elf_b200.ops import fused as Fu
+
+    torch.manual_seed(5)
+    vocab, dim = 500, 512
+    for grad_dtype in (torch.bfloat16, torch.float32):
+        table = torch.nn.Parameter(torch.randn(vocab, dim, device=dev, dtype=torch.bfloat16))
+        ref = torch.zeros(vocab, dim, device=dev, dtype=torch.float32)
+        runs = []
+        for attempt in range(2):
+            buf = torch.zeros(vocab, dim, device=dev, dtype=grad_dtype)
+            if grad_dtype == torch.bfloat16:
+                table.grad = buf
+            else:
+                table.grad, table.main_grad = None, buf
+            gen = torch.Generator(device=dev).manual_seed(11)
+            for mb in range(2):
+                ids = torch.randint(0, 40 if mb == 0 else vocab, (2, 300), device=dev, generator=gen)  # heavy repetition in the first
+                g = torch.randn(2, 300, dim, device=dev, dtype=torch.bfloat16, generator=gen)
+                Fu.embedding(table, ids, into_grad=True).backward(g)
+                if attempt == 0:
+                    ref.index_add_(0, ids.reshape(-1), g.reshape(-1, dim).float())
+            runs.append(buf.clone())
+        assert torch.equal(runs[0], runs[1]), "embedding backward is not deterministic"
+        assert rel_err(runs[0], ref) < (1e-2 if grad_dtype == torch.bfloat16 else 1e-6)
+        if hasattr(table, "main_grad"):
+            del table.main_grad
+
+
 def test_fused_adamw(dev):
     from elf_b200.optim import FusedAdamW
 

@@ -197,6 +197,30 @@ def test_pipeline_memory_budget_end_to_end():
     assert len(out) == 4 and torch.isfinite(loss)
 
 
+def test_pipeline_offload_option_reaches_the_ilp(monkeypatch):
+    """``Pipeline(memory_budget=..., offload=True)`` asks the solver for offload decisions."""
+    import elf_b200.scheduling.ilp as ilp
+
+    seen = {}
+    real = ilp.solve_remat
+
+    def spy(*args, **kwargs):
+        seen.update(kwargs)
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ilp, "solve_remat", spy)
+    torch.manual_seed(0)
+    stages = gpt_stages(GPT(CFG), 2)
+    for s in stages:
+        replace_layer_with_layer_dw(s)
+    ids, tgt = data()
+    pipe = Pipeline(stages, ids[:1], partitioner=False, scheduler="zbv", placement=[0, 0], memory_budget=1e6, offload=True, outputs="device")
+    out, loss = pipe(ids, tgt, GPT.loss_fn, split_size=1)
+    assert seen.get("offload") is True
+    assert "offload" in pipe.scheduler.solution
+    assert len(out) == 4 and torch.isfinite(loss)
+
+
 def test_checkpoint_roundtrip(tmp_path):
     pipe, ref = make("1f1b", [0])
     path = pipe.checkpoint(epoch=3, dir_path=str(tmp_path), extra={"optimizer": {"step": 7}})
