@@ -32,7 +32,8 @@ import torch.distributed as dist
 
 from benchmarks.benchmark_utils import ClockSampler, get_checkpointed_scheduler, get_offloaded_scheduler, init_dist, max_over_ranks, write_detailed_stats
 from elf_b200 import Pipeline, PipelineConfig, Placement, replace_layer_with_layer_dw, sequential_signatures
-from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, llama_loss_fn
+from benchmarks.models.utils import add_transformer_args, model_config_from_args
+from elf_b200.models.llama import LLAMA_CONFIGS, build_llama, build_llama_stages, llama_loss_fn
 from elf_b200.models.simple import ChainTransformer, FullTransformer
 from elf_b200.optim import DummyOptimizer, FusedAdamW, MixedPrecisionOptimizer
 from elf_b200.registry import SCHEDULERS, TRACERS
@@ -43,12 +44,7 @@ _DTYPES = {"float16": torch.float16, "fp16": torch.float16, "bfloat16": torch.bf
 
 def parse_args():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--architecture", default="llama", choices=["llama", "full", "chain"])
-    ap.add_argument("--model", default="llama3-8b", choices=sorted(LLAMA_CONFIGS), help="Llama-family shape")
-    ap.add_argument("--config-file", help="JSON/YAML with a 'model' section; CLI flags win")
-    for flag, typ in [("--input-dim", int), ("--hidden-dim", int), ("--n-blocks", int), ("--seq-len", int), ("--num-heads", int), ("--ffn-dim", int), ("--dropout", float)]:
-        ap.add_argument(flag, type=typ, default=None)
-    ap.add_argument("--dtype", default=None, choices=sorted(_DTYPES))
+    add_transformer_args(ap)  # --architecture, --name/--model, --config-file, dimensions, --dtype, --sdp-backend
     ap.add_argument("--batch-size", type=int, default=None, help="global batch per DP replica")
     ap.add_argument("--nmb", type=int, default=None)
     ap.add_argument("--mb-size", type=int, default=1)
@@ -73,39 +69,36 @@ def parse_args():
     ap.add_argument("--memory-budget", type=int, help="MB per GPU; enables ILP rematerialisation")
     ap.add_argument("--tracer", default="default", choices=TRACERS.available() if len(TRACERS) else ["default"])
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "symm"])
+    ap.add_argument("--check", action="store_true", help="before timing, compare one pipeline step (outputs, loss, every gradient) with the same model run in a single process")
     ap.add_argument("--p2p", default="auto", choices=["auto", "nccl", "copy"], help="stage-to-stage transport")
     ap.add_argument("--offload-ilp", action="store_true", help="with --memory-budget: let the ILP also offload activations to pinned host memory")
     return ap.parse_args()
 
 
-def _merge_config_file(args):
-    if not args.config_file:
-        return
-    with open(args.config_file) as f:
-        if args.config_file.endswith((".yml", ".yaml")):
-            import yaml
+def _with_zoo_api(model, loss_fn, sample, vocab):
+    """Give a model that lacks them the ``get_sample`` / ``get_target`` / ``loss_fn`` members the
+    correctness check calls (the Llama stages are plain ``nn.Sequential``)."""
+    if hasattr(model, "get_sample"):
+        return model
+    shape = tuple(sample.shape[1:])
 
-            cfg = yaml.safe_load(f)
-        else:
-            cfg = json.load(f)
-    for key, value in (cfg.get("model") or {}).items():
-        if key == "name":
-            key = "model"
-        if hasattr(args, key) and getattr(args, key) in (None, ap_default(key)):
-            setattr(args, key, value)
+    def get_sample(n, dtype=None, device="cpu"):
+        return torch.randint(0, vocab, (n, *shape), device=device)
 
-
-def ap_default(key):
-    return {"architecture": "llama", "model": "llama3-8b"}.get(key)
+    model.get_sample, model.get_target, model.loss_fn = get_sample, get_sample, loss_fn
+    return model
 
 
 def main():
     args = parse_args()
-    _merge_config_file(args)
+    if args.architecture is None and not args.config_file:
+        args.architecture = "llama"  # this entry point's default; the option module's own default is "full"
+    mcfg = model_config_from_args(args)
+    args.architecture, args.model = mcfg["architecture"], mcfg["name"]
     local, rank, world = init_dist(args.backend)
     logging.basicConfig(level={"none": 100, "info": logging.INFO, "debug": logging.DEBUG}[args.log])
     device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
-    dtype = _DTYPES[args.dtype or ("bfloat16" if device.type == "cuda" else "float32")]
+    dtype = mcfg["dtype"] if (args.dtype or args.config_file) else (torch.bfloat16 if device.type == "cuda" else torch.float32)
     pp = world // args.dp
     assert args.batch_size is not None or args.nmb is not None, "Batch size or number of micro-batches must be provided"
     batch = args.mb_size * args.nmb if args.batch_size is None else args.batch_size
@@ -123,7 +116,21 @@ def main():
 
     t0 = time.time()
     pp_rank = rank % pp
-    if args.architecture == "llama":
+    if args.architecture == "llama" and args.partitioner != "handcrafted":
+        # graph front end on the Llama model: the worker rank builds the whole decoder as one flat
+        # nn.Sequential of fused blocks, traces it, times every node on its GPU, cuts it with the
+        # chosen partitioner and ships the stages; the other ranks only pass the sample
+        cfg = LLAMA_CONFIGS[args.model]
+        if args.seq_len:
+            from dataclasses import replace as _replace
+
+            cfg = _replace(cfg, seq_len=args.seq_len)
+        model = build_llama(cfg, device=device, dtype=dtype, seed=1234, split_backward=True) if rank == 0 else None
+        parts, signatures, partitioner = model, None, args.partitioner
+        loss_fn, vocab, seq = llama_loss_fn, cfg.vocab, cfg.seq_len
+        sample = torch.randint(0, vocab, (args.mb_size, seq), device=device)
+        n_params = cfg.n_params()
+    elif args.architecture == "llama":
         cfg = LLAMA_CONFIGS[args.model]
         mine = placement.get_ids(pp_rank)
         stages = build_llama_stages(cfg, len(placement), only=mine, device=device, dtype=dtype, seed=1234, placement=list(placement), split_layers=args.split_layers)
@@ -142,7 +149,9 @@ def main():
         sample = torch.randint(0, vocab, (args.mb_size, seq), device=device)
         n_params = cfg.n_params()
     else:
-        kw = {k: getattr(args, k) for k in ("input_dim", "hidden_dim", "n_blocks", "seq_len", "num_heads", "ffn_dim", "dropout") if getattr(args, k) is not None}
+        kw = {k: mcfg[k] for k in ("hidden_dim", "n_blocks", "seq_len", "num_heads", "num_kv_heads", "ffn_dim", "dropout", "sdp_backend")}
+        if args.architecture == "full":
+            kw["input_dim"] = mcfg["input_dim"]
         cls = FullTransformer if args.architecture == "full" else ChainTransformer
         model = cls(**kw).to(dtype)
         replace_layer_with_layer_dw(model)
@@ -158,12 +167,32 @@ def main():
     if budget is not None and not args.no_optimizer:
         budget -= n_params * torch.empty(0, dtype=dtype).element_size() / world / 2**20
     config = PipelineConfig(partitioner=partitioner, scheduler=scheduler, placement=list(placement), tracer=args.tracer, pp=pp, dp=args.dp,
-                            memory_budget=budget, signatures=signatures, outputs="none", grad_sync=args.grad_sync, p2p=args.p2p,
+                            memory_budget=budget, signatures=signatures, outputs="device" if args.check else "none", grad_sync=args.grad_sync, p2p=args.p2p,
                             offload=args.offload_ilp)
     pipe = Pipeline(parts, sample, config=config)
     if world > 1:
         dist.barrier()
     partition_time = time.time() - t0
+    if args.check:
+        if partitioner is False:
+            raise SystemExit("--check needs the un-partitioned model: use an automatic partitioner (--partitioner constrained|naive|metis|dagP)")
+        from benchmarks.benchmark_utils import check_correctness
+
+        reference_model = model if rank == 0 else None
+        if world > 1:  # every rank needs the module (for its sample/target/loss functions); rank 0 holds the real one
+            box = [None]
+            if rank == 0:
+                import copy
+
+                with torch.device("meta"):
+                    skeleton = copy.deepcopy(model).to("meta")
+                box = [skeleton]
+            dist.broadcast_object_list(box, src=0)
+            reference_model = model if rank == 0 else box[0]
+        tol = 1e-3 if dtype == torch.float32 else 5e-2
+        report = check_correctness(_with_zoo_api(reference_model, loss_fn, sample, vocab), pipe, atol=tol, rtol=tol, batch=max(2, pp) * args.mb_size)
+        if report:
+            print(f"correctness check passed: max abs differences {report}")
 
     params = list(pipe.parameters())
     if args.no_optimizer or not params:
@@ -171,11 +200,11 @@ def main():
     elif device.type == "cuda" and dtype == torch.bfloat16 and args.opt_device == "cuda" and args.opt_dtype in (None, "float32", "fp32"):
         opt = FusedAdamW(params, lr=1e-4, eps=1e-5)
     else:
-        opt = MixedPrecisionOptimizer(torch.optim.AdamW, params, dtype, _DTYPES[args.opt_dtype] if args.opt_dtype else dtype, torch.device(args.opt_device), lr=1e-4, eps=1e-5)
+        opt = MixedPrecisionOptimizer(torch.optim.AdamW, params, dtype, _DTYPES[args.opt_dtype] if args.opt_dtype else dtype, torch.device(args.opt_device if device.type == "cuda" else "cpu"), lr=1e-4, eps=1e-5)
 
     def make_batch():
         if args.architecture == "chain":
-            x = torch.randn(batch, seq, args.hidden_dim or 256, dtype=dtype, device=device)
+            x = torch.randn(batch, seq, mcfg["hidden_dim"], dtype=dtype, device=device)
             return x, x.clone()
         tok = torch.randint(0, vocab, (batch, seq + 1), device=device)
         return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
