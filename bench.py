@@ -44,10 +44,12 @@ def parse_args():
     ap.add_argument("--dp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--whole-layers", action="store_true", help="cut stages at layer boundaries only (for comparison)")
+    ap.add_argument("--split-halves", action="store_true", help="cut stages between attention and MLP halves only (default: thirds when they balance the ranks better)")
     ap.add_argument("--split-thirds", action="store_true", help="also allow a stage boundary after the MLP's SwiGLU (two tensors cross it); finer balance for deep pipelines")
     ap.add_argument("--timeline", default=None, help="write every rank's per-operation device timeline of one extra step (JSON) to this file")
+    ap.add_argument("--grad-sync", choices=["auto", "nccl", "symm"], default="auto", help="with --dp > 1: peer-memory gradient exchange fused into the weight-gradient GEMM, or NCCL all-reduce")
     ap.add_argument("--p2p", choices=["auto", "nccl", "copy"], default="auto", help="stage-to-stage transport: NCCL send/recv kernels, or copy-engine writes into the consumer's ring buffer")
-    ap.add_argument("--no-calibrate", action="store_true", help="keep the schedule laid out for the analytic stage costs (for comparison)")
+    ap.add_argument("--no-calibrate", action="store_true", help="cut the stages and lay the schedule out for the built-in cost constants instead of times measured at start-up (for comparison)")
     return ap.parse_args()
 
 
@@ -57,7 +59,7 @@ def run_ours(args):
 
     from benchmarks.benchmark_utils import ClockSampler, init_dist, max_over_ranks
     from elf_b200 import Pipeline, Placement
-    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, head_cost_in_layers, llama_loss_fn, llama_stage_costs, llama_stage_ranges, llama_stage_signatures
+    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, choose_llama_cut, llama_loss_fn, llama_stage_costs, llama_stage_ranges, llama_stage_signatures
     from elf_b200.ops import _ext
     from elf_b200.optim import DummyOptimizer, FusedAdamW
     from dataclasses import replace
@@ -77,12 +79,27 @@ def run_ours(args):
     mine = placement.get_ids(pp_rank)
     # stage boundaries may fall between the attention half and the MLP half of a layer: whole
     # layers cannot balance 32 layers + the LM head (2.2 layers' worth) over 8 ranks
-    split_layers = False if (pp == 1 or args.whole_layers) else ("thirds" if args.split_thirds else True)
-    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, placement=list(placement), split_layers=split_layers)
+    # what an attention half, the two MLP parts, the embedding and the head + loss cost on this GPU,
+    # timed before the model is built (a second or two): the cut balances measured time per rank
+    cost_model = None
+    if pp > 1 and not args.no_calibrate and not args.whole_layers:
+        from elf_b200.models.llama_costs import measure_cost_model
+
+        cost_model = measure_cost_model(cfg, device, mb_size=args.mb_size)
+    if pp == 1 or args.whole_layers:
+        split_layers = False
+    elif args.split_thirds:
+        split_layers = "thirds"
+    elif args.split_halves or cost_model is None:
+        split_layers = True
+    else:
+        split_layers = choose_llama_cut(cfg, len(placement), list(placement), cost_model)
+    cut = dict(placement=list(placement), split_layers=split_layers, cost_model=cost_model)
+    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, **cut)
     parts = [stages[i] for i in mine]
-    stage_costs = llama_stage_costs(cfg, len(placement), list(placement), split_layers)
-    signatures = llama_stage_signatures(cfg, len(placement), list(placement), split_layers)
-    ranges, parts_per_layer, _ = llama_stage_ranges(cfg, len(placement), list(placement), split_layers)
+    stage_costs = llama_stage_costs(cfg, len(placement), **cut)
+    signatures = llama_stage_signatures(cfg, len(placement), **cut)
+    ranges, parts_per_layer, _ = llama_stage_ranges(cfg, len(placement), **cut)
     counts = [round((b - a) / parts_per_layer, 2) for a, b in ranges]
     scheduler, sched_note = args.scheduler, args.scheduler
     if args.scheduler == "zbv" and pp > 1:
@@ -93,9 +110,10 @@ def run_ours(args):
 
         from elf_b200.scheduling.schedulers import generate_zbv_schedule
 
-        scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=stage_costs, ratios=(1.0, 1.25, 0.9))
-        sched_note = "zbv (list-scheduled with per-stage costs, F:B:W = 1:1.25:0.9, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
-    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", signatures=signatures, p2p=args.p2p)
+        ratios = tuple(round(v / cost_model.fbw[0], 3) for v in cost_model.fbw) if cost_model is not None else (1.0, 1.25, 0.9)
+        scheduler = functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=stage_costs, ratios=ratios)
+        sched_note = f"zbv (list-scheduled with per-stage costs, F:B:W = {ratios[0]}:{ratios[1]}:{ratios[2]}, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
+    pipe = Pipeline(parts, None, partitioner=False, scheduler=scheduler, placement=list(placement), dp=dp, outputs="none", signatures=signatures, p2p=args.p2p, grad_sync=args.grad_sync)
     params = list(pipe.parameters())
     opt = FusedAdamW(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-5, weight_decay=0.1) if params else DummyOptimizer()
 
@@ -251,8 +269,10 @@ def run_ours(args):
             "scheduler": sched_note,
             "placement": list(placement),
             "layers_per_stage": counts,
+            "stage_cut": {"split_layers": split_layers, "cost_model": ({k: (round(v, 4) if isinstance(v, float) else v) for k, v in cost_model.to_dict().items()} if cost_model else "built-in constants")},
             "optimizer": "fused AdamW, fp32 master/m/v, step inside the timed region",
             "p2p": (pipe.channels.transport if pipe.channels is not None else "none"),
+            "grad_sync": ("none" if dp == 1 else ("symm (peer-memory push from the weight-gradient GEMM epilogue)" if pipe.grad_sync is not None else "nccl all-reduce")),
             "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed",
         },
         "clocks": clocks.summary(),

@@ -311,7 +311,7 @@ THIRD_SHARES = (ATTENTION_SHARE, 0.55, 0.25)
 
 
 def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0, attention_share: float = ATTENTION_SHARE,
-                      shares: Optional[Sequence[float]] = None):
+                      shares: Optional[Sequence[float]] = None, embed_units: float = 0.0):
     """Split the 2·n_layers half-layers (attention half, MLP half, attention half, ...) into
     ``n_stages`` contiguous ranges so that the busiest *rank* has as little work as possible.
 
@@ -324,12 +324,15 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     move one boundary by one half-layer while that lowers (max rank load, sum of squared loads).
     ``shares`` generalises the unit: a layer is cut into ``len(shares)`` consecutive parts of those
     relative costs (``THIRD_SHARES`` = attention, gate/up + SwiGLU, down projection) and the
-    ranges index those parts."""
+    ranges index those parts.  ``embed_units`` is the cost of the embedding (in layers), carried
+    by the first stage the way ``head_units`` is carried by the last."""
     shares = tuple(shares) if shares is not None else (attention_share, 1.0 - attention_share)
     k = len(shares)
     n_blocks = k * n_layers
     assert n_stages <= n_blocks, "more stages than layer parts"
-    unit = [shares[b % k] for b in range(n_blocks)]
+    total_share = float(sum(shares))
+    unit = [shares[b % k] / total_share for b in range(n_blocks)]
+    unit[0] += embed_units  # the first layer part always sits in stage 0, next to the embedding
     prefix = [0.0]
     for u in unit:
         prefix.append(prefix[-1] + u)
@@ -520,34 +523,60 @@ def _modules_for_range(cfg: LlamaConfig, first: int, last: int, k: int = 2) -> L
     return mods
 
 
-def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers):
-    """(ranges, parts per layer, costs) for ``split_layers`` = False, True / "halves" or "thirds"."""
-    head = head_cost_in_layers(cfg) if placement is not None else 0.0
+def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers, cost_model=None):
+    """(ranges, parts per layer, costs) for ``split_layers`` = False, True / "halves" or "thirds".
+    ``cost_model`` (``elf_b200.models.llama_costs.LlamaCostModel``) replaces the built-in constants
+    for the parts of a layer, the head and the embedding - typically measured on the device."""
+    if cost_model is None:
+        head = head_cost_in_layers(cfg) if placement is not None else 0.0
+        embed, halves, thirds = 0.0, None, THIRD_SHARES
+    else:
+        head = cost_model.head if placement is not None else 0.0
+        embed = cost_model.embed if placement is not None else 0.0
+        halves, thirds = cost_model.shares(2), cost_model.shares(3)
     if split_layers in (True, "halves"):
-        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head)
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=halves, embed_units=embed)
         return ranges, 2, costs
     if split_layers == "thirds":
-        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=THIRD_SHARES)
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=thirds, embed_units=embed)
         return ranges, 3, costs
     assert not split_layers, f"split_layers must be False, True, 'halves' or 'thirds', got {split_layers!r}"
     counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)
     ends = [2 * sum(counts[: i + 1]) for i in range(n_stages)]
     ranges = [(ends[i] - 2 * counts[i], ends[i]) for i in range(n_stages)]
-    return ranges, 2, [c + (head_cost_in_layers(cfg) if i == n_stages - 1 else 0.0) for i, c in enumerate(counts)]
+    head_last = head if placement is not None else head_cost_in_layers(cfg)
+    return ranges, 2, [c + (head_last if i == n_stages - 1 else 0.0) + (embed if i == 0 else 0.0) for i, c in enumerate(counts)]
 
 
-def llama_stage_ranges(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False):
+def choose_llama_cut(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], cost_model=None, gain: float = 0.03):
+    """``split_layers`` value to use for this placement: ``"thirds"`` (a third cut point per layer,
+    after SwiGLU; that boundary carries two tensors) when it lowers the busiest rank's load by more
+    than ``gain`` against cutting between attention and MLP halves only, else ``True``."""
+
+    def busiest(mode):
+        costs = _stage_ranges(cfg, n_stages, list(placement), mode, cost_model)[2]
+        load = {}
+        for s_, c in enumerate(costs):
+            load[placement[s_]] = load.get(placement[s_], 0.0) + c
+        return max(load.values())
+
+    if n_stages > 3 * cfg.n_layers:
+        return True
+    return "thirds" if busiest("thirds") < (1.0 - gain) * busiest(True) else True
+
+
+def llama_stage_ranges(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False, cost_model=None):
     """``(ranges, parts per layer, stage costs)`` of the cut ``build_llama_stages`` makes: ``ranges[s]`` is
     the half-open range of layer parts of stage ``s`` (2 parts per layer, 3 with ``"thirds"``)."""
-    return _stage_ranges(cfg, n_stages, placement, split_layers)
+    return _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)
 
 
-def llama_stage_signatures(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False):
+def llama_stage_signatures(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False, cost_model=None):
     """Signatures of the stages ``build_llama_stages`` cuts: one tensor per boundary, except after a
     gate/up block (``split_layers="thirds"``), where the residual stream and the activation cross."""
     from ..partitioners.signature import Signature
 
-    ranges, k, _ = _stage_ranges(cfg, n_stages, placement, split_layers)
+    ranges, k, _ = _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)
     width = [2 if (k == 3 and last % 3 == 2 and s != n_stages - 1) else 1 for s, (_, last) in enumerate(ranges)]  # tensors leaving stage s
     sigs = []
     for s in range(n_stages):
@@ -559,12 +588,12 @@ def llama_stage_signatures(cfg: LlamaConfig, n_stages: int, placement: Optional[
     return sigs
 
 
-def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False) -> List[float]:
-    """Cost of every stage in decoder-layer units (LM head included), as ``build_llama_stages`` cuts them."""
-    return _stage_ranges(cfg, n_stages, placement, split_layers)[2]
+def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Sequence[int]] = None, split_layers=False, cost_model=None) -> List[float]:
+    """Cost of every stage in decoder-layer units (LM head and embedding included), as ``build_llama_stages`` cuts them."""
+    return _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)[2]
 
 
-def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False) -> List[Optional[LlamaStage]]:
+def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False, cost_model=None) -> List[Optional[LlamaStage]]:
     """Build the stages listed in ``only`` (all by default) directly on ``device``; the
     others are returned as ``None``, so a rank materialises only what it hosts.  Stage ``i``
     is seeded with ``seed + i``: the weights of a stage do not depend on who builds it.
@@ -572,10 +601,12 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
     with ``split_layers`` a stage boundary may also fall between the attention half and the
     MLP half of a layer (see ``half_layer_ranges``), with ``split_layers="thirds"`` also after the
     MLP's SwiGLU, where two tensors cross the boundary (pass ``llama_stage_signatures(...)`` to the
-    pipeline in that case)."""
+    pipeline in that case).  ``cost_model`` (see ``elf_b200.models.llama_costs``) makes the cut for
+    measured block times instead of the built-in constants; pass the same one to
+    ``llama_stage_costs`` / ``llama_stage_signatures`` / ``llama_stage_ranges``."""
     from ..zb_utils import replace_layer_with_layer_dw
 
-    ranges, parts_per_layer, _ = _stage_ranges(cfg, n_stages, placement, split_layers)
+    ranges, parts_per_layer, _ = _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)
     stages: List[Optional[LlamaStage]] = []
     for i, (first, last) in enumerate(ranges):
         if only is not None and i not in only:

@@ -187,3 +187,21 @@ def test_two_tensor_stage_boundary_on_gpu(dev):
             key = n if n in want else n.replace(".layer.", ".")
             err = ((p.grad.float() - want[key].float()).norm() / want[key].float().norm().clamp_min(1e-9)).item()
             assert err < 5e-2, (block.id, n, err)
+
+
+def test_measured_cost_model_on_the_device(dev):
+    """Timing the parts of a (small) layer on the GPU gives a usable cost model: shares of a layer
+    add up to one, every part takes time, the head costs more than a norm would."""
+    from elf_b200.models.llama import LlamaConfig, choose_llama_cut, llama_stage_costs
+    from elf_b200.models.llama_costs import measure_cost_model
+
+    cfg = LlamaConfig(n_layers=8, d_model=512, n_heads=4, n_kv_heads=2, ffn=1536, vocab=4096, seq_len=512, rope_theta=500000.0)
+    cm = measure_cost_model(cfg, dev, mb_size=2, iters=2)
+    assert cm.source == "measured" and cm.layer_ms > 0
+    assert abs(cm.attention + cm.mlp_up + cm.mlp_down - 1.0) < 1e-6
+    assert min(cm.attention, cm.mlp_up, cm.mlp_down, cm.head, cm.embed) > 0
+    assert abs(sum(cm.fbw) - 1.0) < 1e-6 and min(cm.fbw) > 0.05
+    placement = [0, 1, 1, 0]
+    mode = choose_llama_cut(cfg, 4, placement, cm)
+    costs = llama_stage_costs(cfg, 4, placement, mode, cm)
+    assert abs(sum(costs) - (cfg.n_layers + cm.head + cm.embed)) < 1e-6

@@ -1,0 +1,65 @@
+"""Stage cuts of the Llama-style decoder: cost models, where the boundaries fall, which
+granularity is chosen."""
+
+import torch
+
+from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, choose_llama_cut, llama_stage_costs, llama_stage_ranges, llama_stage_signatures
+from elf_b200.models.llama_costs import LlamaCostModel, analytic_cost_model, measure_cost_model
+
+CFG = LLAMA_CONFIGS["llama3-8b"]
+
+
+def v(pp):
+    return list(range(pp)) + list(range(pp - 1, -1, -1))
+
+
+def loads(costs, placement):
+    out = {}
+    for s, c in enumerate(costs):
+        out[placement[s]] = out.get(placement[s], 0.0) + c
+    return [out[r] for r in sorted(out)]
+
+
+def test_cost_model_roundtrip_and_cpu_fallback():
+    cm = analytic_cost_model(CFG)
+    assert abs(cm.attention + cm.mlp_up + cm.mlp_down - 1.0) < 1e-9 and cm.head > 1.0
+    assert LlamaCostModel.from_dict(cm.to_dict()) == cm
+    assert cm.shares(2) == (cm.attention, cm.mlp) and len(cm.shares(3)) == 3
+    assert measure_cost_model(CFG, "cpu").source == "analytic"
+
+
+def test_a_costlier_embedding_moves_work_off_the_first_rank():
+    pl = v(8)
+    light = LlamaCostModel(0.2, 0.55, 0.25, head=1.0, embed=0.0)
+    heavy = LlamaCostModel(0.2, 0.55, 0.25, head=1.0, embed=0.8)
+    r_light = llama_stage_ranges(CFG, 16, pl, "thirds", light)[0]
+    r_heavy = llama_stage_ranges(CFG, 16, pl, "thirds", heavy)[0]
+    parts = lambda r: (r[0][1] - r[0][0]) + (r[15][1] - r[15][0])  # layer parts on rank 0 (first and last stage)
+    assert parts(r_heavy) < parts(r_light)
+    for ranges in (r_light, r_heavy):  # contiguous cover of all 96 parts
+        assert ranges[0][0] == 0 and ranges[-1][1] == 3 * CFG.n_layers
+        assert all(a[1] == b[0] and a[1] > a[0] for a, b in zip(ranges, ranges[1:]))
+    costs = llama_stage_costs(CFG, 16, pl, "thirds", heavy)
+    assert abs(sum(costs) - (CFG.n_layers + 1.0 + 0.8)) < 1e-6
+    ld = loads(costs, pl)
+    assert max(ld) / (sum(ld) / len(ld)) < 1.05
+
+
+def test_cut_granularity_follows_the_balance():
+    cm = LlamaCostModel(0.2, 0.55, 0.25, head=1.0, embed=0.3)
+    assert choose_llama_cut(CFG, 16, v(8), cm) == "thirds"  # halves leave one rank 10 % above the mean
+    assert choose_llama_cut(CFG, 4, v(2), cm) is True  # two ranks balance with halves already
+    # signatures and built stages agree with the chosen ranges
+    small = LLAMA_CONFIGS["llama-tiny"]
+    pl = v(2)
+    mode = "thirds"
+    sigs = llama_stage_signatures(small, 4, pl, mode, cm)
+    stages = build_llama_stages(small, 4, device="cpu", dtype=torch.float32, placement=pl, split_layers=mode, cost_model=cm)
+    x = torch.randint(0, small.vocab, (2, small.seq_len))
+    out = (x,)
+    for sig, stage in zip(sigs, stages):
+        assert len(sig.inputs) == len(out)
+        y = stage(*out)
+        out = y if isinstance(y, tuple) else (y,)
+        assert len(sig.outputs) == len(out)
+    assert out[0].shape == (2, small.seq_len, small.vocab)
