@@ -49,10 +49,13 @@ at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tens
   c10::cuda::CUDAGuard g(x.device());
   const int dim = (int)x.size(-1);
   const int rows = (int)(x.numel() / dim);
-  TORCH_CHECK(dw.scalar_type() == at::kFloat && dw.numel() == dim && dw.is_contiguous(), "dw must be fp32 [dim]");
+  const bool dw_bf16 = dw.scalar_type() == at::kBFloat16;
+  TORCH_CHECK((dw.scalar_type() == at::kFloat || dw_bf16) && dw.is_cuda() && dw.numel() == dim && dw.is_contiguous(), "dw must be a contiguous fp32 or bf16 [dim] CUDA tensor");
+  TORCH_CHECK(!dw_bf16 || accumulate_dw, "a bf16 dw is a gradient buffer: it can only be accumulated into");
   const int nb = elfb::rmsnorm_backward_blocks(rows);
   at::Tensor part = (scratch.has_value() && scratch->defined()) ? *scratch : at::empty({(int64_t)nb * dim}, x.options().dtype(at::kFloat));
-  TORCH_CHECK(part.numel() >= (int64_t)nb * dim && part.scalar_type() == at::kFloat, "scratch too small");
+  TORCH_CHECK(part.scalar_type() == at::kFloat && part.is_contiguous() && part.numel() >= (int64_t)elfb::rmsnorm_backward_min_blocks() * dim, "scratch too small");
+  const int scratch_rows = (int)(part.numel() / dim);
   auto dx = at::empty_like(x);
   const void* dr = nullptr;
   if (dres.has_value() && dres->defined()) {
@@ -60,9 +63,19 @@ at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tens
     dr = dres->data_ptr();
   }
   check(elfb::rmsnorm_backward(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(),
-                               part.data_ptr<float>(), dw.data_ptr<float>(), accumulate_dw, rows, dim, cur()),
+                               part.data_ptr<float>(), scratch_rows, dw.data_ptr(), dw_bf16, accumulate_dw, rows, dim, cur()),
         "rmsnorm_backward");
   return dx;
+}
+
+// out += res in place; returns out
+at::Tensor residual_add(at::Tensor& out, const at::Tensor& res) {
+  need_bf16(out, "out");
+  need_bf16(res, "res");
+  TORCH_CHECK(out.numel() == res.numel() && out.numel() % 8 == 0, "residual_add needs equally sized tensors with a multiple of 8 elements");
+  c10::cuda::CUDAGuard g(out.device());
+  check(elfb::residual_add(out.data_ptr(), res.data_ptr(), out.numel(), cur()), "residual_add");
+  return out;
 }
 
 void rope_(at::Tensor& x, const at::Tensor& cos_t, const at::Tensor& sin_t, int64_t n_rot_heads, int64_t head_dim,
@@ -125,6 +138,34 @@ void ce_bwd(const at::Tensor& logits, at::Tensor& out, const at::Tensor& targets
   check(elfb::cross_entropy_backward(logits.data_ptr(), out.data_ptr(), targets.data_ptr<int64_t>(), lse.data_ptr<float>(), gs,
                                      (float)scale, (int)logits.size(0), (int)logits.size(1), logits.stride(0), ignore_index, cur()),
         "cross_entropy_backward");
+}
+
+void ce_chunk_stats(const at::Tensor& logits, const at::Tensor& targets, at::Tensor& run_max, at::Tensor& run_sum, at::Tensor& tgt_logit, int64_t col0,
+                    bool first) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be a 2-D bf16 CUDA matrix");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0), "one int64 target per row");
+  for (const at::Tensor* t : {&run_max, &run_sum, &tgt_logit})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == logits.size(0), "row statistics must be fp32 [rows]");
+  c10::cuda::CUDAGuard g(logits.device());
+  check(elfb::cross_entropy_chunk_stats(logits.data_ptr(), targets.data_ptr<int64_t>(), run_max.data_ptr<float>(), run_sum.data_ptr<float>(),
+                                        tgt_logit.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), logits.stride(0), col0, first, cur()),
+        "cross_entropy_chunk_stats");
+}
+
+void ce_chunk_grad(at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse, const c10::optional<at::Tensor>& gscale, double scale,
+                   int64_t col0, int64_t vocab, int64_t ignore_index) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1, "logits must be a 2-D bf16 CUDA matrix");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0), "one int64 target per row");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == logits.size(0), "lse must be fp32 [rows]");
+  const float* gs = nullptr;
+  if (gscale.has_value() && gscale->defined()) {
+    TORCH_CHECK(gscale->scalar_type() == at::kFloat && gscale->numel() == 1 && gscale->is_cuda(), "gscale must be one fp32 value on the device");
+    gs = gscale->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard g(logits.device());
+  check(elfb::cross_entropy_chunk_grad(logits.data_ptr(), targets.data_ptr<int64_t>(), lse.data_ptr<float>(), gs, (float)scale, (int)logits.size(0),
+                                       (int)logits.size(1), logits.stride(0), col0, vocab, ignore_index, cur()),
+        "cross_entropy_chunk_grad");
 }
 
 at::Tensor embedding_fwd(const at::Tensor& table, const at::Tensor& ids) {
@@ -196,11 +237,16 @@ void register_fused_ops(pybind11::module_& m) {
   m.def("rmsnorm_bwd_blocks", &elfb::rmsnorm_backward_blocks);
   m.def("rope_", &rope_, py::arg("x"), py::arg("cos"), py::arg("sin"), py::arg("n_rot_heads"), py::arg("head_dim"),
         py::arg("seq_len"), py::arg("backward") = false);
+  m.def("residual_add", &residual_add, "out += res (bf16, in place); returns out");
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("ce_fwd", &ce_fwd, py::arg("logits"), py::arg("targets"), py::arg("ignore_index") = -100);
   m.def("ce_bwd", &ce_bwd, py::arg("logits"), py::arg("out"), py::arg("targets"), py::arg("lse"), py::arg("gscale") = c10::nullopt,
         py::arg("scale") = 1.0, py::arg("ignore_index") = -100);
+  m.def("ce_chunk_stats", &ce_chunk_stats, py::arg("logits"), py::arg("targets"), py::arg("run_max"), py::arg("run_sum"), py::arg("tgt_logit"),
+        py::arg("col0"), py::arg("first"));
+  m.def("ce_chunk_grad", &ce_chunk_grad, py::arg("logits"), py::arg("targets"), py::arg("lse"), py::arg("gscale") = c10::nullopt, py::arg("scale") = 1.0,
+        py::arg("col0") = 0, py::arg("vocab") = 0, py::arg("ignore_index") = -100);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("embedding_bwd_sorted", &embedding_bwd_sorted);

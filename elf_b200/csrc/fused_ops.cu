@@ -5,6 +5,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 namespace elfb {
 
 namespace {
@@ -224,6 +226,170 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
   out[c] = accumulate ? out[c] + s : s;
 }
 
+// Persistent variants for the common widths (dim = 256 * VPT * 8: 2048, 4096, 8192).  A block of
+// 256 threads walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; thread t always owns the same
+// VPT 16-byte column groups (t, t + 256, ...), so the gain stays in registers, the loads of the
+// next row are issued before the current row is reduced (reads and writes of different rows
+// overlap instead of alternating), and - in the backward - the gain's gradient is accumulated
+// in registers over all rows of the block: one pass over dy and x instead of two.
+template <bool RESIDUAL, int VPT>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_persistent_kernel(const Bf16x8* __restrict__ x, const Bf16x8* __restrict__ res,
+                                                                     const Bf16x8* __restrict__ w, Bf16x8* __restrict__ y,
+                                                                     Bf16x8* __restrict__ h, float* __restrict__ rstd, int rows,
+                                                                     float inv_dim, float eps) {
+  constexpr int DIM8 = 256 * VPT;
+  __shared__ float red[32];
+  float wv[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) unpack8(w[threadIdx.x + v * 256], wv[v]);
+  long long row = blockIdx.x;
+  Bf16x8 nx[VPT], nr[VPT];
+  if (row < rows) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      nx[v] = x[row * DIM8 + threadIdx.x + v * 256];
+      if (RESIDUAL) nr[v] = res[row * DIM8 + threadIdx.x + v * 256];
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
+    float vals[VPT][8];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      unpack8(nx[v], vals[v]);
+      if (RESIDUAL) {
+        float r[8];
+        unpack8(nr[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[v][j] += r[j];
+      }
+    }
+    const long long next = row + gridDim.x;
+    if (next < rows) {  // prefetch the next row of this block
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        nx[v] = x[next * DIM8 + threadIdx.x + v * 256];
+        if (RESIDUAL) nr[v] = res[next * DIM8 + threadIdx.x + v * 256];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      if (RESIDUAL) {
+        const Bf16x8 hv = pack8(vals[v]);
+        h[row * DIM8 + threadIdx.x + v * 256] = hv;
+        unpack8(hv, vals[v]);  // normalise exactly what later passes will read back
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[v][j] * vals[v][j];
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss * inv_dim + eps);
+    if (threadIdx.x == 0) rstd[row] = rs;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[v][j] * rs * wv[v][j];
+      y[row * DIM8 + threadIdx.x + v * 256] = pack8(o);
+    }
+  }
+}
+
+template <bool DRES, int VPT>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_persistent_kernel(const Bf16x8* __restrict__ dy, const Bf16x8* __restrict__ x,
+                                                                     const Bf16x8* __restrict__ w, const float* __restrict__ rstd,
+                                                                     const Bf16x8* __restrict__ dres, Bf16x8* __restrict__ dx,
+                                                                     float* __restrict__ dw_partial, int rows, float inv_dim) {
+  constexpr int DIM8 = 256 * VPT;
+  __shared__ float red[32];
+  float wv[VPT][8], dwacc[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    unpack8(w[threadIdx.x + v * 256], wv[v]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[v][j] = 0.f;
+  }
+  long long row = blockIdx.x;
+  Bf16x8 ng[VPT], nx[VPT], nr[VPT];
+  if (row < rows) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      ng[v] = dy[row * DIM8 + threadIdx.x + v * 256];
+      nx[v] = x[row * DIM8 + threadIdx.x + v * 256];
+      if (DRES) nr[v] = dres[row * DIM8 + threadIdx.x + v * 256];
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
+    float gv[VPT][8], xv[VPT][8], rv[VPT][8];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      unpack8(ng[v], gv[v]);
+      unpack8(nx[v], xv[v]);
+      if (DRES) unpack8(nr[v], rv[v]);
+    }
+    const float rs = rstd[row];
+    const long long next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        ng[v] = dy[next * DIM8 + threadIdx.x + v * 256];
+        nx[v] = x[next * DIM8 + threadIdx.x + v * 256];
+        if (DRES) nr[v] = dres[next * DIM8 + threadIdx.x + v * 256];
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dwacc[v][j] += gv[v][j] * xv[v][j] * rs;
+        gv[v][j] *= wv[v][j];
+        dot += gv[v][j] * xv[v][j];
+      }
+    }
+    dot = block_sum(dot, red);
+    const float c = dot * inv_dim * rs * rs * rs;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = gv[v][j] * rs - xv[v][j] * c;
+        if (DRES) o[j] += rv[v][j];
+      }
+      dx[row * DIM8 + threadIdx.x + v * 256] = pack8(o);
+    }
+  }
+  // one partial row per block: dw_partial[blockIdx.x][dim]
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float* dst = dw_partial + ((long long)blockIdx.x * DIM8 + threadIdx.x + v * 256) * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
+  }
+}
+
+// Same reduction, added into a bf16 vector (a parameter's gradient buffer) in fp32.
+__global__ void colsum_add_bf16_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nblocks, int dim) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float s = __bfloat162float(out[c]);
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * dim + c];
+  out[c] = __float2bfloat16_rn(s);
+}
+
+// out[i] += res[i] (bf16, fp32 add): the residual connection after a projection
+__global__ void residual_add_kernel(Bf16x8* __restrict__ out, const Bf16x8* __restrict__ res, long long n8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float a[8], b[8];
+  unpack8(out[i], a);
+  unpack8(res[i], b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] += b[j];
+  out[i] = pack8(a);
+}
+
 // ------------------------------------------------------------------------------ RoPE
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                             long long total, int row_stride, int n_rot_heads, int half, int seq_len, float sign) {
@@ -358,6 +524,82 @@ __global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(const __nv_bfloat16*
   for (int i = v8 * 8 + threadIdx.x; i < vocab; i += CE_THREADS) {
     const float p = __expf(__bfloat162float(lr[i]) - l);
     dr[i] = __float2bfloat16((p - (i == t ? 1.f : 0.f)) * g);
+  }
+}
+
+// Cross entropy over the vocabulary in chunks: the LM head's logits never exist as a whole.
+// `logits` holds the columns [col0, col0 + width) of every row.  The statistics kernel folds the
+// chunk into the running (max, sum of exp, target logit) of each row; once all chunks are in,
+// lse = max + log(sum) and loss = lse - target logit.  The gradient kernel turns a (recomputed)
+// chunk into (softmax - onehot) * scale in place.
+__global__ void __launch_bounds__(CE_THREADS) ce_chunk_stats_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                                                                    float* __restrict__ run_max, float* __restrict__ run_sum,
+                                                                    float* __restrict__ tgt_logit, int width, long long ld, long long col0,
+                                                                    bool first) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  const int v8 = width / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < v8; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(lr)[i], f);
+    float cm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) cm = fmaxf(cm, f[j]);
+    const float nm = fmaxf(m, cm);
+    float add = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + add;
+    m = nm;
+  }
+  for (int i = v8 * 8 + threadIdx.x; i < width; i += CE_THREADS) {
+    const float f = __bfloat162float(lr[i]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  const float gm = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float pm = first ? -INFINITY : run_max[row];
+    const float ps = first ? 0.f : run_sum[row];
+    const float nm = fmaxf(pm, gm);
+    run_sum[row] = (pm == -INFINITY ? 0.f : ps * __expf(pm - nm)) + gs * __expf(gm - nm);
+    run_max[row] = nm;
+    const long long t = targets[row] - col0;
+    if (first) tgt_logit[row] = 0.f;
+    if (t >= 0 && t < width) tgt_logit[row] = __bfloat162float(lr[t]);
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS) ce_chunk_grad_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                                                                   const float* __restrict__ lse, const float* __restrict__ gscale, float scale,
+                                                                   int width, long long ld, long long col0, long long vocab,
+                                                                   int64_t ignore_index) {
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const int64_t t = targets[row];
+  const bool ignored = (t == ignore_index || t < 0 || t >= vocab);
+  const float g = ignored ? 0.f : (gscale ? gscale[0] : 1.f) * scale;
+  const float l = lse[row];
+  const long long tl = t - col0;  // target column inside this chunk, if any
+  const int v8 = width / 8;
+  for (int i = threadIdx.x; i < v8; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const Bf16x8*>(lr)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = __expf(f[j] - l);
+      f[j] = (p - ((long long)i * 8 + j == tl ? 1.f : 0.f)) * g;
+    }
+    reinterpret_cast<Bf16x8*>(lr)[i] = pack8(f);
+  }
+  for (int i = v8 * 8 + threadIdx.x; i < width; i += CE_THREADS) {
+    const float p = __expf(__bfloat162float(lr[i]) - l);
+    lr[i] = __float2bfloat16((p - (i == tl ? 1.f : 0.f)) * g);
   }
 }
 
@@ -502,11 +744,34 @@ inline int blocks_for(long long n, int threads) { return (int)((n + threads - 1)
 
 // ------------------------------------------------------------------------------ launchers
 
+// The persistent RMSNorm kernels run with a fixed number of 256-thread blocks (a few per SM)
+// however many rows there are; ELFB_RMS_PERSISTENT=0 selects the one-block-per-row kernels.
+static const bool g_rms_persistent = []() {
+  const char* e = getenv("ELFB_RMS_PERSISTENT");
+  return !(e && e[0] == '0');
+}();
+constexpr int RMS_FWD_BLOCKS = 592;  // 4 per SM on 148 SMs (64 registers per thread at dim 4096)
+constexpr int RMS_BWD_BLOCKS = 296;  // 2 per SM (128 registers per thread); also the scratch rows the backward writes
+static inline int rms_persistent_grid(int rows, int blocks) { return rows < blocks ? (rows > 0 ? rows : 1) : blocks; }
+
 cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, void* y, void* h, float* rstd, int rows,
                             int dim, float eps, cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
   if (dim % 8) return cudaErrorInvalidValue;
   const int dim8 = dim / 8;
+  if (g_rms_persistent && (dim == 2048 || dim == 4096 || dim == 8192)) {
+    const int grid = rms_persistent_grid(rows, RMS_FWD_BLOCKS);
+    const Bf16x8 *xp = (const Bf16x8*)x, *rp = (const Bf16x8*)residual, *wp = (const Bf16x8*)w;
+    Bf16x8 *yp = (Bf16x8*)y, *hp = (Bf16x8*)h;
+#define ELFB_RMS_FWD(RES, VPT) rmsnorm_fwd_persistent_kernel<RES, VPT><<<grid, 256, 0, s>>>(xp, rp, wp, yp, hp, rstd, rows, 1.f / dim, eps)
+    if (residual) {
+      if (dim == 2048) ELFB_RMS_FWD(true, 1); else if (dim == 4096) ELFB_RMS_FWD(true, 2); else ELFB_RMS_FWD(true, 4);
+    } else {
+      if (dim == 2048) ELFB_RMS_FWD(false, 1); else if (dim == 4096) ELFB_RMS_FWD(false, 2); else ELFB_RMS_FWD(false, 4);
+    }
+#undef ELFB_RMS_FWD
+    return cudaGetLastError();
+  }
   const bool narrow = dim8 <= 128 * RMS_MAX_VEC;
   if (residual) {
     if (narrow)
@@ -524,13 +789,41 @@ cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, 
   return cudaGetLastError();
 }
 
-int rmsnorm_backward_blocks(int rows) { return RMS_DW_SPLITS; }
+// Scratch rows (of `dim` floats) the backward wants: the persistent kernel writes one partial row
+// per block.  With fewer rows available (but at least rmsnorm_backward_min_blocks()) the
+// one-block-per-row kernels run instead.
+int rmsnorm_backward_blocks(int rows) {
+  const int g = rms_persistent_grid(rows, RMS_BWD_BLOCKS);
+  return g > RMS_DW_SPLITS ? g : RMS_DW_SPLITS;
+}
+int rmsnorm_backward_min_blocks() { return RMS_DW_SPLITS; }
 
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
-                             float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s) {
+                             float* dw_partial, int scratch_rows, void* dw, bool dw_bf16, bool accumulate_dw, int rows, int dim,
+                             cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  if (dim % 8 || dim > 256 * RMS_MAX_VEC * 8) return cudaErrorInvalidValue;
+  if (dim % 8 || dim > 256 * RMS_MAX_VEC * 8 || scratch_rows < RMS_DW_SPLITS) return cudaErrorInvalidValue;
   const int dim8 = dim / 8;
+  if (g_rms_persistent && (dim == 2048 || dim == 4096 || dim == 8192) && scratch_rows >= rms_persistent_grid(rows, RMS_BWD_BLOCKS)) {
+    const int grid = rms_persistent_grid(rows, RMS_BWD_BLOCKS);
+    const Bf16x8 *gp = (const Bf16x8*)dy, *xp = (const Bf16x8*)x, *wp = (const Bf16x8*)w, *rp = (const Bf16x8*)dres_in;
+#define ELFB_RMS_BWD(RES, VPT) rmsnorm_bwd_persistent_kernel<RES, VPT><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, (Bf16x8*)dx, dw_partial, rows, 1.f / dim)
+    if (dres_in) {
+      if (dim == 2048) ELFB_RMS_BWD(true, 1); else if (dim == 4096) ELFB_RMS_BWD(true, 2); else ELFB_RMS_BWD(true, 4);
+    } else {
+      if (dim == 2048) ELFB_RMS_BWD(false, 1); else if (dim == 4096) ELFB_RMS_BWD(false, 2); else ELFB_RMS_BWD(false, 4);
+    }
+#undef ELFB_RMS_BWD
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (dw_bf16) {
+      if (!accumulate_dw) return cudaErrorInvalidValue;
+      colsum_add_bf16_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (__nv_bfloat16*)dw, grid, dim);
+    } else {
+      colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (float*)dw, grid, dim, accumulate_dw);
+    }
+    return cudaGetLastError();
+  }
   const bool narrow = dim8 <= 128 * RMS_MAX_VEC;
   if (dres_in) {
     if (narrow)
@@ -551,7 +844,19 @@ cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const
   rmsnorm_bwd_dw_kernel<<<grid, 256, 0, s>>>((const Bf16x8*)dy, (const Bf16x8*)x, rstd, dw_partial, rows, dim8);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, dw, RMS_DW_SPLITS, dim, accumulate_dw);
+  if (dw_bf16) {
+    if (!accumulate_dw) return cudaErrorInvalidValue;  // a bf16 target is a gradient buffer: always added to
+    colsum_add_bf16_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (__nv_bfloat16*)dw, RMS_DW_SPLITS, dim);
+  } else {
+    colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (float*)dw, RMS_DW_SPLITS, dim, accumulate_dw);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t residual_add(void* out, const void* res, long long n, cudaStream_t s) {
+  if (n % 8) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  residual_add_kernel<<<blocks_for(n / 8, 256), 256, 0, s>>>((Bf16x8*)out, (const Bf16x8*)res, n / 8);
   return cudaGetLastError();
 }
 
@@ -595,6 +900,21 @@ cudaError_t cross_entropy_backward(const void* logits, void* dlogits, const int6
   if (ld % 8) return cudaErrorInvalidValue;
   ce_bwd_kernel<<<rows, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, (__nv_bfloat16*)dlogits, targets, lse, gscale, scale,
                                             vocab, ld, ignore_index);
+  return cudaGetLastError();
+}
+
+cudaError_t cross_entropy_chunk_stats(const void* logits, const int64_t* targets, float* run_max, float* run_sum, float* tgt_logit, int rows,
+                                      int width, long long ld, long long col0, bool first, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (ld % 8) return cudaErrorInvalidValue;
+  ce_chunk_stats_kernel<<<rows, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, targets, run_max, run_sum, tgt_logit, width, ld, col0, first);
+  return cudaGetLastError();
+}
+cudaError_t cross_entropy_chunk_grad(void* logits, const int64_t* targets, const float* lse, const float* gscale, float scale, int rows, int width,
+                                     long long ld, long long col0, long long vocab, int64_t ignore_index, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (ld % 8) return cudaErrorInvalidValue;
+  ce_chunk_grad_kernel<<<rows, CE_THREADS, 0, s>>>((__nv_bfloat16*)logits, targets, lse, gscale, scale, width, ld, col0, vocab, ignore_index);
   return cudaGetLastError();
 }
 

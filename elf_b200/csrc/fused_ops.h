@@ -11,10 +11,17 @@ namespace elfb {
 cudaError_t rmsnorm_forward(const void* x, const void* residual, const void* w, void* y, void* h, float* rstd, int rows,
                             int dim, float eps, cudaStream_t s);
 // dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) [+ dres_in]; dw_partial[group][dim] = sum over a group of rows of dy*x*rstd.
-// `dw_partial` is scratch of rmsnorm_backward_blocks(rows) * dim floats; `dw` (fp32 [dim]) receives (+=) the column sums.
+// `dw_partial` is scratch of rmsnorm_backward_blocks(rows) * dim floats; `dw` ([dim]) receives (+=) the column sums:
+// fp32, written or accumulated, or bf16 (`dw_bf16`, a gradient buffer, accumulate only; the sum is formed in fp32).
+// `scratch_rows` says how many rows of `dim` floats `dw_partial` holds: rmsnorm_backward_blocks(rows) selects the
+// single-pass persistent kernel, rmsnorm_backward_min_blocks() is the least that works (two-pass kernels).
 int rmsnorm_backward_blocks(int rows);
+int rmsnorm_backward_min_blocks();
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
-                             float* dw_partial, float* dw, bool accumulate_dw, int rows, int dim, cudaStream_t s);
+                             float* dw_partial, int scratch_rows, void* dw, bool dw_bf16, bool accumulate_dw, int rows, int dim,
+                             cudaStream_t s);
+// out[i] += res[i] over n bf16 elements (n % 8 == 0): the residual add after a projection, in place.
+cudaError_t residual_add(void* out, const void* res, long long n, cudaStream_t s);
 
 // In-place rotary embedding on the first `n_rot_heads` heads of a [rows][n_heads*head_dim] bf16 matrix;
 // position = row % seq_len; cos/sin tables are fp32 [seq_len][head_dim/2]; sign = +1 forward, -1 backward.
@@ -35,6 +42,13 @@ cudaError_t cross_entropy_backward(const void* logits, void* dlogits, const int6
                                    cudaStream_t s);
 
 // out[row] = table[ids[row]]
+// Cross entropy with the vocabulary processed in column chunks.  `logits` = columns [col0, col0 + width) of all rows
+// (row pitch `ld` elements).  stats: fold the chunk into run_max / run_sum (sum of exp(x - run_max)) / tgt_logit per row
+// (`first` initialises them).  grad: logits <- (exp(logits - lse) - [col == target]) * scale * gscale, in place.
+cudaError_t cross_entropy_chunk_stats(const void* logits, const int64_t* targets, float* run_max, float* run_sum, float* tgt_logit, int rows,
+                                      int width, long long ld, long long col0, bool first, cudaStream_t s);
+cudaError_t cross_entropy_chunk_grad(void* logits, const int64_t* targets, const float* lse, const float* gscale, float scale, int rows, int width,
+                                     long long ld, long long col0, long long vocab, int64_t ignore_index, cudaStream_t s);
 cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s);
 // dtable[ids[row]] += dout[row]   (fp32 or bf16 table gradient; atomics)
 // grad[sorted_ids[k]] += dout[perm[k]] for every k, deterministically: equal ids are adjacent in

@@ -61,7 +61,7 @@ extern "C" int elfb_rmsnorm_backward_noalloc(const void* dy, const void* x, cons
     snprintf(detail, sizeof(detail), "dim %d exceeds the built-in scratch (maximum %d)", dim, ELFB_NOALLOC_MAX_DIM);
     return fail(ELFB_NOALLOC_BAD_SIZE, detail);
   }
-  if ((size_t)elfb::rmsnorm_backward_blocks(rows) * (size_t)dim * sizeof(float) > (size_t)ELFB_NOALLOC_SCRATCH_BYTES)
+  if ((size_t)elfb::rmsnorm_backward_min_blocks() * (size_t)dim * sizeof(float) > (size_t)ELFB_NOALLOC_SCRATCH_BYTES)
     return fail(ELFB_NOALLOC_BAD_SIZE, "problem does not fit the built-in scratch");
   if (rows == 0) return ELFB_NOALLOC_OK;
   if (!dy || !x || !w || !rstd || !dx || !dw) return fail(ELFB_NOALLOC_BAD_POINTER, "null pointer argument");
@@ -70,7 +70,8 @@ extern "C" int elfb_rmsnorm_backward_noalloc(const void* dy, const void* x, cons
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != ELFB_NOALLOC_OK) return rc;
-  const cudaError_t e = elfb::rmsnorm_backward(dy, x, w, rstd, /*dres_in=*/nullptr, dx, scratch, dw, /*accumulate_dw=*/false, rows, dim,
+  const cudaError_t e = elfb::rmsnorm_backward(dy, x, w, rstd, /*dres_in=*/nullptr, dx, scratch, /*scratch_rows=*/(int)((size_t)ELFB_NOALLOC_SCRATCH_BYTES / sizeof(float) / (size_t)dim), dw, /*dw_bf16=*/false,
+                                               /*accumulate_dw=*/false, rows, dim,
                                                static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(ELFB_NOALLOC_CUDA_ERROR, "kernel launch failed: ", cudaGetErrorString(e));
   return ELFB_NOALLOC_OK;

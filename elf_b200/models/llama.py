@@ -20,6 +20,8 @@ against.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import asdict, dataclass
 from typing import List, Optional, Sequence
 
@@ -28,6 +30,7 @@ import torch.nn as nn
 
 from ..ops import attention as _attn
 from ..ops import fused as _f
+from . import llama_fused as _fused
 
 __all__ = [
     "LlamaConfig",
@@ -44,6 +47,11 @@ __all__ = [
     "layers_per_stage",
     "head_cost_in_layers",
 ]
+
+
+# Whole layers / half layers as one autograd node each (see ``llama_fused``); ``ELF_B200_FUSED_LAYERS=0``
+# keeps the chain of small autograd functions (numerics A/B, debugging).
+FUSED_LAYERS = os.environ.get("ELF_B200_FUSED_LAYERS", "1") != "0"
 
 
 @dataclass
@@ -122,7 +130,11 @@ class LlamaDecoderLayer(nn.Module):
             self._rope = _f.rope_tables(max(seq_len, self.seq_len), self.head_dim, self.theta, device)
         return self._rope
 
+    fused = FUSED_LAYERS  # one autograd node with a hand-written backward (elf_b200.models.llama_fused)
+
     def forward(self, x):
+        if self.fused and _fused.fused_apply(x, self.wqkv, self.wo, self.w_gate_up, self.w_down):
+            return _fused.decoder_layer(self, x)
         b, s, d = x.shape
         hq, hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         cos, sin = self._tables(x.device, s)
@@ -152,8 +164,11 @@ class LlamaAttentionBlock(nn.Module):
         self._rope = None
 
     _tables = LlamaDecoderLayer._tables
+    fused = FUSED_LAYERS
 
     def forward(self, x):
+        if self.fused and _fused.fused_apply(x, self.wqkv, self.wo):
+            return _fused.attention_half(self, x)
         b, s, d = x.shape
         hq, hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         cos, sin = self._tables(x.device, s)
@@ -175,7 +190,11 @@ class LlamaMLPBlock(nn.Module):
         self.w_gate_up = nn.Linear(d, 2 * cfg.ffn, bias=False)
         self.w_down = nn.Linear(cfg.ffn, d, bias=False)
 
+    fused = FUSED_LAYERS
+
     def forward(self, x):
+        if self.fused and _fused.fused_apply(x, self.w_gate_up, self.w_down):
+            return _fused.mlp_half(self, x)
         return x + self.w_down(_f.swiglu(self.w_gate_up(self.norm2(x))))
 
 
@@ -208,15 +227,21 @@ class LlamaMLPDownBlock(nn.Module):
 
 
 class LlamaHead(nn.Module):
+    """Final norm + vocabulary projection.  With ``fused_loss`` the projection is left to the loss
+    function (``elf_b200.ops.head_loss.ChunkedHeadLoss(head)``), which walks the vocabulary in chunks
+    and never holds the logits: ``forward`` then returns the normalised hidden states."""
+
     _elf_leaf = True
 
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, fused_loss: bool = False):
         super().__init__()
         self.norm = RMSNorm(cfg.d_model, cfg.eps)
         self.out = nn.Linear(cfg.d_model, cfg.vocab, bias=False)
+        self.fused_loss = fused_loss
 
     def forward(self, x):
-        return self.out(self.norm(x))
+        h = self.norm(x)
+        return h if self.fused_loss else self.out(h)
 
 
 class LlamaStage(nn.Sequential):

@@ -378,3 +378,118 @@ def test_smoke_entry(dev):
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+def test_attention_at_the_benchmark_shape(dev):
+    """B=1, S=4096, 32 query / 8 KV heads (the Llama-3-8B layer): all 148 CTAs persistent, 32 key
+    tiles per head.  The fp32 formula is evaluated on a sample of heads only (the full score
+    matrix would be 2 GB per head group); forward output, log-sum-exp and all three gradients."""
+    from elf_b200.ops import attention_native as A
+    from elf_b200.ops import gemm as G
+
+    torch.manual_seed(11)
+    seq, hq, hkv = 4096, 32, 8
+    qkv = torch.randn(1, seq, hq + 2 * hkv, 128, device=dev).bfloat16()
+    g = torch.randn(1, seq, hq, 128, device=dev).bfloat16()
+    out, lse = A.forward_packed(qkv, hq, hkv)
+    dqkv = A.backward_packed(g, qkv, out, lse, hq, hkv)
+    G.check_status(dev)
+    group = hq // hkv
+    for kv in (0, 5, 7):  # first, a middle and the last KV head, with the 4 query heads that share it
+        heads = list(range(kv * group, (kv + 1) * group))
+        sub = torch.cat([qkv[:, :, heads], qkv[:, :, hq + kv : hq + kv + 1], qkv[:, :, hq + hkv + kv : hq + hkv + kv + 1]], dim=2).float().requires_grad_()
+        ref_out, ref_lse = _attention_reference(sub, group, 1)
+        assert rel_err(out[:, :, heads], ref_out) < 1e-2
+        assert (lse[:, heads] - ref_lse).abs().max().item() < 2e-2
+        ref_out.backward(g[:, :, heads].float())
+        want = sub.grad
+        assert rel_err(dqkv[:, :, heads], want[:, :, :group]) < 2e-2  # dQ
+        assert rel_err(dqkv[:, :, hq + kv], want[:, :, group]) < 2e-2  # dK, summed over the group
+        assert rel_err(dqkv[:, :, hq + hkv + kv], want[:, :, group + 1]) < 2e-2  # dV
+
+
+def test_residual_add_and_norm_gain_gradient_into_bf16(dev):
+    from elf_b200.ops import _ext
+
+    ext = _ext.get()
+    torch.manual_seed(2)
+    a = torch.randn(300, 4096, device=dev, dtype=torch.bfloat16)
+    b = torch.randn_like(a)
+    want = (a.float() + b.float()).bfloat16()
+    got = ext.residual_add(a, b)
+    assert got.data_ptr() == a.data_ptr() and torch.equal(got, want)
+    # RMSNorm backward adding the gain's gradient to a bf16 buffer that already holds something
+    x = torch.randn(300, 4096, device=dev).bfloat16()
+    dy = torch.randn_like(x)
+    w = (1 + 0.1 * torch.randn(4096, device=dev)).bfloat16()
+    _, rstd, _ = ext.rmsnorm_fwd(x, w, 1e-5, None)
+    dw32 = torch.empty(4096, device=dev, dtype=torch.float32)
+    dx_ref = ext.rmsnorm_bwd(dy, x, w, rstd, dw32, False, None, None)
+    buf = torch.full((4096,), 0.5, device=dev, dtype=torch.bfloat16)
+    dx = ext.rmsnorm_bwd(dy, x, w, rstd, buf, True, None, None)
+    assert torch.equal(dx, dx_ref)
+    assert rel_err(buf, dw32 + 0.5) < 5e-3
+    with pytest.raises(RuntimeError, match="only be accumulated"):
+        ext.rmsnorm_bwd(dy, x, w, rstd, buf, False, None, None)
+
+
+@pytest.mark.parametrize("block", ["layer", "attention", "mlp"])
+def test_single_node_layer_matches_the_composed_layer(dev, block):
+    """The hand-written backward (one autograd node per layer or half layer) against the same
+    module run as a chain of small autograd functions: output, input gradient, the W-pass
+    operands it files and every parameter gradient after the W pass."""
+    from elf_b200.models import llama as L
+    from elf_b200.zb_utils import LayerDW, replace_layer_with_layer_dw
+
+    cfg = L.LlamaConfig(n_layers=1, d_model=512, n_heads=4, n_kv_heads=2, ffn=1536, vocab=1024, seq_len=256, rope_theta=500000.0)
+    cls = {"layer": L.LlamaDecoderLayer, "attention": L.LlamaAttentionBlock, "mlp": L.LlamaMLPBlock}[block]
+    results = {}
+    for fused in (False, True):
+        torch.manual_seed(0)
+        with torch.device(dev):
+            m = cls(cfg).to(torch.bfloat16)
+        L.init_llama_(m, 0.02, 3)
+        replace_layer_with_layer_dw(m)
+        m.fused = fused
+        x = torch.randn(2, cfg.seq_len, cfg.d_model, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).bfloat16().requires_grad_()
+        g = torch.randn(2, cfg.seq_len, cfg.d_model, device=dev, generator=torch.Generator(device=dev).manual_seed(2)).bfloat16()
+        layers = [mod for mod in m.modules() if isinstance(mod, LayerDW)]
+        for mb in range(2):  # two micro-batches: gradients accumulate
+            y = m(x)
+            for layer in layers:
+                layer.move_last_computed("input", mb)
+            y.backward(g)
+            for layer in layers:
+                layer.move_last_computed("grad_output", mb)
+        for mb in range(2):
+            for layer in layers:
+                layer.backward(mb)
+        results[fused] = (y.detach(), x.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()})
+    (y0, dx0, g0), (y1, dx1, g1) = results[False], results[True]
+    assert rel_err(y1, y0) < 2e-3
+    assert rel_err(dx1, dx0) < 1e-2
+    assert set(g0) == set(g1)
+    for name in g0:
+        assert rel_err(g1[name], g0[name]) < 1e-2, name
+
+
+def test_chunked_head_loss_matches_the_plain_head(dev):
+    """LM head + cross entropy with the vocabulary in chunks (ragged last chunk, an ignored row)
+    against fp32 logits: loss, hidden-state gradient, weight gradient added to what is there."""
+    from elf_b200.ops.head_loss import chunked_head_loss
+
+    torch.manual_seed(4)
+    rows, d, vocab = 300, 512, 5000 * 8 // 8 + 8  # 5008: not a multiple of the chunk
+    h = (torch.randn(rows, d, device=dev) * 0.5).bfloat16().requires_grad_()
+    w = torch.nn.Parameter((torch.randn(vocab, d, device=dev) * 0.05).bfloat16())
+    w.grad = torch.full_like(w, 0.25)
+    t = torch.randint(0, vocab, (rows,), device=dev)
+    t[7] = -100
+    loss = chunked_head_loss(h, w, t, reduction="sum", chunk=1024)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    ref = F.cross_entropy(hf @ wf.t(), t, reduction="sum", ignore_index=-100)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * abs(ref.item())
+    assert rel_err(h.grad, hf.grad) < 2e-2
+    assert rel_err(w.grad.float() - 0.25, wf.grad) < 2e-2

@@ -49,7 +49,16 @@ def test_no_alloc_entry_point_matches_regular_path_twice():
     torch.cuda.set_device(dev)
     lib = _load()
     stream = torch.cuda.current_stream(dev)
-    for call, (rows, dim, seed) in enumerate([(300, 4096, 11), (77, 1024, 12)]):
+    # set-up call: the first use on a device resolves the scratch array's address, and the driver
+    # gives the library's static array (2 MiB) its memory when the module is first used; from then
+    # on no call may change the amount of free device memory
+    x0, dy0, w0, rstd0 = _case(8, 64, 1, dev)
+    dx0, dw0 = torch.empty_like(x0), torch.empty(64, device=dev)
+    assert lib.elfb_rmsnorm_backward_noalloc(dy0.data_ptr(), x0.data_ptr(), w0.data_ptr(), rstd0.data_ptr(), dx0.data_ptr(), dw0.data_ptr(), 8, 64, stream.cuda_stream) == 0
+    torch.cuda.synchronize(dev)
+    # the second case is the documented maximum width (whole scratch array, wide-row kernel variant);
+    # the third, narrower one would show scratch contents left over from it
+    for call, (rows, dim, seed) in enumerate([(300, 4096, 11), (70, 8192, 13), (77, 1024, 12)]):
         x, dy, w, rstd = _case(rows, dim, seed, dev)
         # regular entry point: scratch comes from torch's allocator
         dw_ref = torch.empty(dim, device=dev, dtype=torch.float32)
@@ -59,10 +68,12 @@ def test_no_alloc_entry_point_matches_regular_path_twice():
         dw = torch.full((dim,), float("nan"), device=dev, dtype=torch.float32)
         torch.cuda.synchronize(dev)
         before = torch.cuda.memory_allocated(dev)
+        free_before, _ = torch.cuda.mem_get_info(dev)  # the driver's view: sees a cudaMalloc that torch's counters cannot
         rc = lib.elfb_rmsnorm_backward_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), rows, dim, stream.cuda_stream)
         assert rc == 0, lib.elfb_noalloc_last_error().decode()
         torch.cuda.synchronize(dev)
         assert torch.cuda.memory_allocated(dev) == before
+        assert torch.cuda.mem_get_info(dev)[0] >= free_before, "device memory was allocated behind the entry point"
         torch.testing.assert_close(dx.float(), dx_ref.float(), atol=1e-2, rtol=1e-2, msg=lambda m: f"call {call}: dx {m}")
         torch.testing.assert_close(dw, dw_ref, atol=1e-2, rtol=1e-2, msg=lambda m: f"call {call}: dw {m}")
         # and against plain fp32 math, like the other kernel tests
@@ -83,5 +94,8 @@ def test_no_alloc_entry_point_rejects_what_does_not_fit():
     assert b"maximum 8192" in lib.elfb_noalloc_last_error()
     assert lib.elfb_rmsnorm_backward_noalloc(*args, 8, 60, None) == -1
     assert lib.elfb_rmsnorm_backward_noalloc(None, *args[1:], 8, 64, None) == -2
+    assert lib.elfb_rmsnorm_backward_noalloc(args[0] + 2, *args[1:], 8, 64, None) == -2  # pointer off its 16-byte boundary
+    assert b"aligned" in lib.elfb_noalloc_last_error()
+    assert lib.elfb_rmsnorm_backward_noalloc(*args, 0, 64, None) == 0  # no rows: nothing to do, nothing launched
     assert lib.elfb_rmsnorm_backward_noalloc(*args, 8, 64, None) == 0
     torch.cuda.synchronize(dev)
