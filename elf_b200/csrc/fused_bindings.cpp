@@ -68,6 +68,33 @@ at::Tensor rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tens
   return dx;
 }
 
+// dq [B,S,hq,D], dk / dv [B,S,hkv,D] (any batch / seq / head strides, D contiguous) -> packed [B,S,hq+2hkv,D]
+at::Tensor pack_qkv_grad(const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv, const c10::optional<at::Tensor>& cos_t,
+                         const c10::optional<at::Tensor>& sin_t) {
+  for (const at::Tensor* t : {&dq, &dk, &dv})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->dim() == 4 && t->stride(3) == 1, "dq, dk, dv must be 4-D bf16 CUDA tensors with a contiguous last dimension");
+  TORCH_CHECK(dk.sizes() == dv.sizes() && dq.size(0) == dk.size(0) && dq.size(1) == dk.size(1) && dq.size(3) == dk.size(3), "shape mismatch");
+  c10::cuda::CUDAGuard g(dq.device());
+  const int64_t B = dq.size(0), S = dq.size(1), hq = dq.size(2), hkv = dk.size(2), D = dq.size(3);
+  auto out = at::empty({B, S, hq + 2 * hkv, D}, dq.options());
+  const long long qs[3] = {dq.stride(0), dq.stride(1), dq.stride(2)}, ks[3] = {dk.stride(0), dk.stride(1), dk.stride(2)},
+                  vs[3] = {dv.stride(0), dv.stride(1), dv.stride(2)};
+  for (const at::Tensor* t : {&dq, &dk, &dv}) TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "gradients must be 16-byte aligned");
+  const float *cp = nullptr, *sp = nullptr;
+  if (cos_t.has_value() && cos_t->defined()) {
+    TORCH_CHECK(sin_t.has_value() && sin_t->defined(), "cos and sin tables come together");
+    for (const at::Tensor* t : {&*cos_t, &*sin_t})
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->dim() == 2 && t->size(0) >= S && t->size(1) == D / 2,
+                  "cos/sin tables must be contiguous fp32 [>= seq, head_dim / 2]");
+    cp = cos_t->data_ptr<float>();
+    sp = sin_t->data_ptr<float>();
+  }
+  check(elfb::pack_qkv_grad(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), out.data_ptr(), (int)B, (int)S, (int)hq, (int)hkv, (int)D, qs, ks, vs, cp, sp,
+                            cur()),
+        "pack_qkv_grad");
+  return out;
+}
+
 // out += res in place; returns out
 at::Tensor residual_add(at::Tensor& out, const at::Tensor& res) {
   need_bf16(out, "out");
@@ -237,6 +264,8 @@ void register_fused_ops(pybind11::module_& m) {
   m.def("rmsnorm_bwd_blocks", &elfb::rmsnorm_backward_blocks);
   m.def("rope_", &rope_, py::arg("x"), py::arg("cos"), py::arg("sin"), py::arg("n_rot_heads"), py::arg("head_dim"),
         py::arg("seq_len"), py::arg("backward") = false);
+  m.def("pack_qkv_grad", &pack_qkv_grad, "pack dq, dk, dv ([B,S,H,D] views) into the fused-QKV gradient layout, optionally applying RoPE's backward",
+        py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("cos") = c10::nullopt, py::arg("sin") = c10::nullopt);
   m.def("residual_add", &residual_add, "out += res (bf16, in place); returns out");
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

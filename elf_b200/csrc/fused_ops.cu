@@ -369,13 +369,104 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_persistent_kernel(const Bf16x
   }
 }
 
-// Same reduction, added into a bf16 vector (a parameter's gradient buffer) in fp32.
+// Column sums of a tall `partial[nrows][dim]` (one row per block of the persistent backward): a block
+// of 256 threads covers 32 columns with 8 row lanes, so the few hundred rows are read by
+// dim/32 blocks in parallel instead of one thread walking each column.  OUT is float
+// (written or accumulated) or bf16 (a gradient buffer: always accumulated, in fp32).
+template <typename OUT>
+__global__ void __launch_bounds__(256) colsum_tall_kernel(const float* __restrict__ partial, OUT* __restrict__ out, int nrows, int dim, bool accumulate) {
+  __shared__ float red[8][32];
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int lane_r = threadIdx.x >> 5;
+  float s = 0.f;
+  if (col < dim)
+    for (int r = lane_r; r < nrows; r += 8) s += partial[(long long)r * dim + col];
+  red[lane_r][threadIdx.x & 31] = s;
+  __syncthreads();
+  if (lane_r == 0 && col < dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += red[r][threadIdx.x];
+    if constexpr (sizeof(OUT) == 2) {
+      out[col] = __float2bfloat16_rn(__bfloat162float(out[col]) + t);
+    } else {
+      out[col] = accumulate ? out[col] + t : t;
+    }
+  }
+}
+
+// Same reduction as colsum_kernel, added into a bf16 vector (a parameter's gradient buffer) in fp32.
 __global__ void colsum_add_bf16_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nblocks, int dim) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= dim) return;
   float s = __bfloat162float(out[c]);
   for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * dim + c];
   out[c] = __float2bfloat16_rn(s);
+}
+
+// dqkv[b, s, :, :] <- (dq[b, s, hq heads], dk[b, s, hkv heads], dv[b, s, hkv heads]): one pass that packs the three
+// gradients an attention backward returns (any strides with a contiguous head dimension) into the
+// layout of the fused QKV projection.  One thread moves 16 bytes.
+// The same packing with RoPE's backward applied on the way: query and key heads are rotated by
+// -angle(position).  One thread moves the two 16-byte groups (i, i + head_dim/2) of a rotation pair.
+__global__ void __launch_bounds__(256) pack_qkv_grad_rope_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+                                                                 const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ out,
+                                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, long long total,
+                                                                 int seq, int hq, int hkv, int half, long long q_sb, long long q_ss, long long q_sh,
+                                                                 long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                                                                 long long v_sh) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int heads = hq + 2 * hkv;
+  const int vph = half / 8;  // 16-byte groups per half head
+  const int v = idx % vph;
+  const int h = (idx / vph) % heads;
+  const long long bs = idx / ((long long)vph * heads);
+  const long long s_ = bs % seq, b = bs / seq;
+  const __nv_bfloat16* src;
+  if (h < hq) src = dq + b * q_sb + s_ * q_ss + h * q_sh;
+  else if (h < hq + hkv) src = dk + b * k_sb + s_ * k_ss + (h - hq) * k_sh;
+  else src = dv + b * v_sb + s_ * v_ss + (h - hq - hkv) * v_sh;
+  __nv_bfloat16* dst = out + (bs * heads + h) * (2LL * half);
+  const Bf16x8 lo = *reinterpret_cast<const Bf16x8*>(src + v * 8), hi = *reinterpret_cast<const Bf16x8*>(src + half + v * 8);
+  if (h >= hq + hkv) {  // value heads: no rotation
+    *reinterpret_cast<Bf16x8*>(dst + v * 8) = lo;
+    *reinterpret_cast<Bf16x8*>(dst + half + v * 8) = hi;
+    return;
+  }
+  float a[8], bb[8], oa[8], ob[8];
+  unpack8(lo, a);
+  unpack8(hi, bb);
+  const float4* c4 = reinterpret_cast<const float4*>(cos_t + s_ * half + v * 8);
+  const float4* s4 = reinterpret_cast<const float4*>(sin_t + s_ * half + v * 8);
+  const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+  const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sj = -sn[j];  // backward of a rotation is the rotation by the opposite angle
+    oa[j] = a[j] * cs[j] - bb[j] * sj;
+    ob[j] = bb[j] * cs[j] + a[j] * sj;
+  }
+  *reinterpret_cast<Bf16x8*>(dst + v * 8) = pack8(oa);
+  *reinterpret_cast<Bf16x8*>(dst + half + v * 8) = pack8(ob);
+}
+
+__global__ void __launch_bounds__(256) pack_qkv_grad_kernel(const Bf16x8* __restrict__ dq, const Bf16x8* __restrict__ dk, const Bf16x8* __restrict__ dv,
+                                                            Bf16x8* __restrict__ out, long long total, int seq, int hq, int hkv, int d8,
+                                                            long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                                                            long long k_sh, long long v_sb, long long v_ss, long long v_sh) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int heads = hq + 2 * hkv;
+  const int c = idx % d8;
+  const int h = (idx / d8) % heads;
+  const long long bs = idx / ((long long)d8 * heads);
+  const long long s_ = bs % seq, b = bs / seq;
+  // strides are in elements of 8 bf16
+  if (h < hq) out[idx] = dq[b * q_sb + s_ * q_ss + h * q_sh + c];
+  else if (h < hq + hkv) out[idx] = dk[b * k_sb + s_ * k_ss + (h - hq) * k_sh + c];
+  else out[idx] = dv[b * v_sb + s_ * v_ss + (h - hq - hkv) * v_sh + c];
 }
 
 // out[i] += res[i] (bf16, fp32 add): the residual connection after a projection
@@ -818,9 +909,9 @@ cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const
     if (e != cudaSuccess) return e;
     if (dw_bf16) {
       if (!accumulate_dw) return cudaErrorInvalidValue;
-      colsum_add_bf16_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (__nv_bfloat16*)dw, grid, dim);
+      colsum_tall_kernel<__nv_bfloat16><<<(dim + 31) / 32, 256, 0, s>>>(dw_partial, (__nv_bfloat16*)dw, grid, dim, true);
     } else {
-      colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (float*)dw, grid, dim, accumulate_dw);
+      colsum_tall_kernel<float><<<(dim + 31) / 32, 256, 0, s>>>(dw_partial, (float*)dw, grid, dim, accumulate_dw);
     }
     return cudaGetLastError();
   }
@@ -850,6 +941,32 @@ cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const
   } else {
     colsum_kernel<<<blocks_for(dim, 256), 256, 0, s>>>(dw_partial, (float*)dw, RMS_DW_SPLITS, dim, accumulate_dw);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t pack_qkv_grad(const void* dq, const void* dk, const void* dv, void* out, int batch, int seq, int hq, int hkv, int head_dim,
+                          const long long* q_strides, const long long* k_strides, const long long* v_strides, const float* cos_t,
+                          const float* sin_t, cudaStream_t s) {
+  if (head_dim % 8) return cudaErrorInvalidValue;
+  for (int i = 0; i < 3; ++i)
+    if (q_strides[i] % 8 || k_strides[i] % 8 || v_strides[i] % 8) return cudaErrorInvalidValue;
+  if (cos_t != nullptr) {
+    const int half = head_dim / 2;
+    if (half % 8 || sin_t == nullptr) return cudaErrorInvalidValue;
+    const long long n = (long long)batch * seq * (hq + 2 * hkv) * (half / 8);
+    if (n == 0) return cudaSuccess;
+    pack_qkv_grad_rope_kernel<<<blocks_for(n, 256), 256, 0, s>>>((const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv,
+                                                                 (__nv_bfloat16*)out, cos_t, sin_t, n, seq, hq, hkv, half, q_strides[0], q_strides[1],
+                                                                 q_strides[2], k_strides[0], k_strides[1], k_strides[2], v_strides[0], v_strides[1],
+                                                                 v_strides[2]);
+    return cudaGetLastError();
+  }
+  const int d8 = head_dim / 8;
+  const long long total = (long long)batch * seq * (hq + 2 * hkv) * d8;
+  if (total == 0) return cudaSuccess;
+  pack_qkv_grad_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)dq, (const Bf16x8*)dk, (const Bf16x8*)dv, (Bf16x8*)out, total, seq, hq, hkv, d8,
+                                                              q_strides[0] / 8, q_strides[1] / 8, q_strides[2] / 8, k_strides[0] / 8, k_strides[1] / 8,
+                                                              k_strides[2] / 8, v_strides[0] / 8, v_strides[1] / 8, v_strides[2] / 8);
   return cudaGetLastError();
 }
 

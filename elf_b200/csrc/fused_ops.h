@@ -20,6 +20,13 @@ int rmsnorm_backward_min_blocks();
 cudaError_t rmsnorm_backward(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in, void* dx,
                              float* dw_partial, int scratch_rows, void* dw, bool dw_bf16, bool accumulate_dw, int rows, int dim,
                              cudaStream_t s);
+// out[b, s, 0:hq] = dq, out[b, s, hq:hq+hkv] = dk, out[b, s, hq+hkv:] = dv for bf16 tensors given as [batch, seq, heads, head_dim]
+// views with element strides {batch, seq, head} (head_dim contiguous; all strides multiples of 8): packs an attention backward's
+// three gradients into the fused-QKV layout in one pass.  With `cos_t` / `sin_t` (fp32 [>= seq, head_dim / 2] tables) the
+// backward of RoPE is applied to the query and key heads on the way (position = index along `seq`).
+cudaError_t pack_qkv_grad(const void* dq, const void* dk, const void* dv, void* out, int batch, int seq, int hq, int hkv, int head_dim,
+                          const long long* q_strides, const long long* k_strides, const long long* v_strides, const float* cos_t,
+                          const float* sin_t, cudaStream_t s);
 // out[i] += res[i] over n bf16 elements (n % 8 == 0): the residual add after a projection, in place.
 cudaError_t residual_add(void* out, const void* res, long long n, cudaStream_t s);
 

@@ -325,6 +325,8 @@ class PipelineBlock:
     # ------------------------------------------------------------------ gradients
     def scale_grads(self, batch_size: int) -> None:
         """Divide every gradient by the number of samples of the step."""
+        if batch_size == 1:
+            return
         inv = 1.0 / batch_size
         for p in self.model.parameters():
             if p.grad is not None:

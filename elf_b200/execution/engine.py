@@ -67,13 +67,16 @@ def preallocate_pool(pool: PinnedHostTensorPool, spec: Optional[str] = None) -> 
             logger.warning("ELF_PREALLOCATE_POOL: cannot parse %r (expected e.g. 'bf16:8,f32:2')", item)
 
 
-def compute_loss(block: PipelineBlock, output: torch.Tensor, target: torch.Tensor, loss_fn: Callable):
+def compute_loss(block: PipelineBlock, output: torch.Tensor, target: torch.Tensor, loss_fn: Callable, grad_scale: float = 1.0):
     """Loss of one micro-batch and a closure that back-propagates it to ``output``.
 
     ``loss_fn`` is called with ``reduction="sum"`` (or without the keyword if it does not
     accept it) and the result is divided by the number of target elements per sample;
     the pipeline later divides by the batch size, which makes the step loss the mean over
-    all elements of all samples."""
+    all elements of all samples.  ``grad_scale`` multiplies what is back-propagated (not the
+    returned loss): with ``1 / batch size`` every gradient of the step comes out already
+    scaled for the mean loss, and the separate pass over all gradients that the reference
+    makes at the end of the step (``elf/execution/block.py:518-527``) is not needed."""
     leaf = output.detach().requires_grad_()
     timer = Timer(name="loss_forward")
     block.compute_time.append(timer)
@@ -86,7 +89,7 @@ def compute_loss(block: PipelineBlock, output: torch.Tensor, target: torch.Tenso
     loss = loss / per_sample
 
     def grad_fn():
-        loss.backward()
+        (loss if grad_scale == 1.0 else loss * grad_scale).backward()
         return (leaf.grad.data,)
 
     return loss.detach(), grad_fn
@@ -120,7 +123,8 @@ class Engine:
             T.RECOMPUTE_FORWARD: lambda b, op: b.recompute_forward(op.mb_id, **op.options),
             T.RECOMPUTE_BACKWARD_INPUTS: lambda b, op: b.recompute_backward_inputs(op.mb_id, **op.options),
             T.PREFETCH_ACTIVATIONS: lambda b, op: self._offloader(b.id, op.mb_id).prefetch(),
-            T.ALL_REDUCE_PARAM_GRADS: lambda b, op: b.sync_grads(self._batch_size),
+            # gradients are born scaled by 1 / batch size (see compute_loss): only the replica average is left
+            T.ALL_REDUCE_PARAM_GRADS: lambda b, op: b.sync_grads(1),
         }
 
     # ------------------------------------------------------------------ op handlers
@@ -183,7 +187,7 @@ class Engine:
             return
         assert op.mb_id in self._results, f"Loss forward for mb {op.mb_id} before its forward"
         assert self._targets is not None, "a target is required on the rank that owns the last stage"
-        loss, grad_fn = compute_loss(block, self._results[op.mb_id][0], self._targets[op.mb_id], self._loss_fn)
+        loss, grad_fn = compute_loss(block, self._results[op.mb_id][0], self._targets[op.mb_id], self._loss_fn, 1.0 / self._batch_size)
         self._losses[op.mb_id] = loss
         self._grad_fns[op.mb_id] = grad_fn
 

@@ -96,14 +96,18 @@ def _attention_forward(qkv: torch.Tensor, hq: int, hkv: int):
     return res[0].transpose(1, 2), _LIBRARY, (res[1], res[6], res[7])  # output, log-sum-exp, philox seed / offset
 
 
-def _attention_backward(g: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, mode: int, saved, hq: int, hkv: int) -> torch.Tensor:
-    """Packed ``dqkv`` for the output gradient ``g [B, S, hq, D]``."""
+def _attention_backward(g: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, mode: int, saved, hq: int, hkv: int, cos, sin) -> torch.Tensor:
+    """Packed ``dqkv`` for the output gradient ``g [B, S, hq, D]``, with RoPE's backward applied to its
+    query and key heads (fused into the packing pass when the library returns three tensors)."""
     if mode == _NATIVE:
         from ..ops import attention_native as _n
 
         (lse,) = saved
         if _n._BACKWARD == "native":
-            return _n.backward_packed(g.contiguous(), qkv, out.contiguous(), lse, hq, hkv)
+            dqkv = _n.backward_packed(g.contiguous(), qkv, out.contiguous(), lse, hq, hkv)
+            b, s, heads, hd = dqkv.shape
+            _ext.get().rope_(dqkv.view(b * s, heads * hd), cos, sin, hq + hkv, hd, s, True)  # in place: this gradient is ours
+            return dqkv
         dq, dk, dv = _n._library_backward(g.contiguous(), qkv, out, lse, hq, hkv, 1.0 / math.sqrt(qkv.shape[-1]))
     else:
         lse, seed, offset = saved
@@ -115,11 +119,7 @@ def _attention_backward(g: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, m
             g.transpose(1, 2), q, k, v, out.transpose(1, 2), lse, seed, offset, None, None, None, s, s, 0.0, True
         )
         dq, dk, dv = dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)
-    dqkv = torch.empty_like(qkv)
-    dqkv[:, :, :hq].copy_(dq)
-    dqkv[:, :, hq : hq + hkv].copy_(dk)
-    dqkv[:, :, hq + hkv :].copy_(dv)
-    return dqkv
+    return _ext.get().pack_qkv_grad(dq, dk, dv, cos, sin)  # one pass: fused-QKV layout + RoPE backward
 
 
 # ---------------------------------------------------------------------------------------
@@ -154,9 +154,8 @@ def _attn_backward_body(blk, x, mode, saved, dy: torch.Tensor) -> torch.Tensor:
     cos, sin = blk._tables(x.device, s)
     blk.wo._accumulate_grad_output(dy)
     d_a = _gemm.linear_input_grad(dy, blk.wo.weight)
-    dqkv = _attention_backward(d_a.view(b, s, hq, hd), qkv, a.view(b, s, hq, hd), mode, saved[3:], hq, hkv)
+    dqkv = _attention_backward(d_a.view(b, s, hq, hd), qkv, a.view(b, s, hq, hd), mode, saved[3:], hq, hkv, cos, sin)
     dqkv2 = dqkv.view(b * s, (hq + 2 * hkv) * hd)
-    ext.rope_(dqkv2, cos, sin, hq + hkv, hd, s, True)  # in place: this gradient is ours
     blk.wqkv._accumulate_grad_output(dqkv2)
     d_h1 = _gemm.linear_input_grad(dqkv2, blk.wqkv.weight)
     # norm backward + the residual branch's gradient in one pass; the gain's gradient goes

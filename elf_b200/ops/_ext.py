@@ -44,7 +44,7 @@ def available() -> bool:
 # kernels ran inside a timed region.
 _LAUNCHES_PER_CALL = {
     "gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 3, "rope_": 1, "swiglu_fwd": 1, "swiglu_bwd": 1, "ce_fwd": 1,
-    "ce_bwd": 1, "embedding_fwd": 1, "residual_add": 1, "ce_chunk_stats": 1, "ce_chunk_grad": 1, "embedding_bwd": 1, "embedding_bwd_sorted": 1, "adamw": 1, "scale_": 1, "attention_fwd": 1,
+    "ce_bwd": 1, "embedding_fwd": 1, "residual_add": 1, "pack_qkv_grad": 1, "ce_chunk_stats": 1, "ce_chunk_grad": 1, "embedding_bwd": 1, "embedding_bwd_sorted": 1, "adamw": 1, "scale_": 1, "attention_fwd": 1,
     "attention_bwd": 3, "push_reduce": 1, "push_ranges": 1, "finalize_reduce": 1, "p2p_signal": 1, "p2p_wait": 1, "gemm_dw_reduce": 1,
 }
 launch_count = 0
