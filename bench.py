@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--split-halves", action="store_true", help="cut stages between attention and MLP halves only (default: thirds when they balance the ranks better)")
     ap.add_argument("--split-thirds", action="store_true", help="also allow a stage boundary after the MLP's SwiGLU (two tensors cross it); finer balance for deep pipelines")
     ap.add_argument("--timeline", default=None, help="write every rank's per-operation device timeline of one extra step (JSON) to this file")
+    ap.add_argument("--chunked-head", action="store_true", help="LM head + cross entropy with the vocabulary in chunks: the logits (1 GB per micro-batch) are never materialised, at the price of one more pass over the head's matrix")
     ap.add_argument("--grad-sync", choices=["auto", "nccl", "symm"], default="auto", help="with --dp > 1: peer-memory gradient exchange fused into the weight-gradient GEMM, or NCCL all-reduce")
     ap.add_argument("--p2p", choices=["auto", "nccl", "copy"], default="auto", help="stage-to-stage transport: NCCL send/recv kernels, or copy-engine writes into the consumer's ring buffer")
     ap.add_argument("--no-calibrate", action="store_true", help="cut the stages and lay the schedule out for the built-in cost constants instead of times measured at start-up (for comparison)")
@@ -95,7 +96,7 @@ def run_ours(args):
     else:
         split_layers = choose_llama_cut(cfg, len(placement), list(placement), cost_model)
     cut = dict(placement=list(placement), split_layers=split_layers, cost_model=cost_model)
-    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, **cut)
+    stages = build_llama_stages(cfg, len(placement), only=mine, device=device, seed=1234, fused_head_loss=args.chunked_head, **cut)
     parts = [stages[i] for i in mine]
     stage_costs = llama_stage_costs(cfg, len(placement), **cut)
     signatures = llama_stage_signatures(cfg, len(placement), **cut)
@@ -126,9 +127,15 @@ def run_ours(args):
         tok = tok.to(device, non_blocking=True)
         return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
 
+    loss_fn = llama_loss_fn
+    if args.chunked_head and stages[-1] is not None:
+        from elf_b200.ops.head_loss import ChunkedHeadLoss
+
+        loss_fn = ChunkedHeadLoss(stages[-1][-1])
+
     def step(ids, tgt):
         opt.zero_grad()
-        _, loss = pipe(ids, tgt, llama_loss_fn, split_size=args.mb_size)
+        _, loss = pipe(ids, tgt, loss_fn, split_size=args.mb_size)
         opt.step()
         return loss
 
@@ -271,6 +278,7 @@ def run_ours(args):
             "layers_per_stage": counts,
             "stage_cut": {"split_layers": split_layers, "cost_model": ({k: (round(v, 4) if isinstance(v, float) else v) for k, v in cost_model.to_dict().items()} if cost_model else "built-in constants")},
             "optimizer": "fused AdamW, fp32 master/m/v, step inside the timed region",
+            "lm_head": "vocabulary-chunked head + cross entropy (no logits tensor)" if args.chunked_head else "head GEMM + cross-entropy kernels over bf16 logits",
             "p2p": (pipe.channels.transport if pipe.channels is not None else "none"),
             "grad_sync": ("none" if dp == 1 else ("symm (peer-memory push from the weight-gradient GEMM epilogue)" if pipe.grad_sync is not None else "nccl all-reduce")),
             "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed",

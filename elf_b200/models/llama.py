@@ -618,7 +618,8 @@ def llama_stage_costs(cfg: LlamaConfig, n_stages: int, placement: Optional[Seque
     return _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)[2]
 
 
-def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False, cost_model=None) -> List[Optional[LlamaStage]]:
+def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[int]] = None, device=None, dtype=torch.bfloat16, seed: int = 0, split_backward: bool = True, placement: Optional[Sequence[int]] = None, split_layers: bool = False, cost_model=None,
+                       fused_head_loss: bool = False) -> List[Optional[LlamaStage]]:
     """Build the stages listed in ``only`` (all by default) directly on ``device``; the
     others are returned as ``None``, so a rank materialises only what it hosts.  Stage ``i``
     is seeded with ``seed + i``: the weights of a stage do not depend on who builds it.
@@ -628,7 +629,9 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
     MLP's SwiGLU, where two tensors cross the boundary (pass ``llama_stage_signatures(...)`` to the
     pipeline in that case).  ``cost_model`` (see ``elf_b200.models.llama_costs``) makes the cut for
     measured block times instead of the built-in constants; pass the same one to
-    ``llama_stage_costs`` / ``llama_stage_signatures`` / ``llama_stage_ranges``."""
+    ``llama_stage_costs`` / ``llama_stage_signatures`` / ``llama_stage_ranges``.  With
+    ``fused_head_loss`` the last stage ends with the final norm only and the vocabulary projection
+    happens inside the loss (``elf_b200.ops.head_loss.ChunkedHeadLoss(stage[-1])`` as loss function)."""
     from ..zb_utils import replace_layer_with_layer_dw
 
     ranges, parts_per_layer, _ = _stage_ranges(cfg, n_stages, placement, split_layers, cost_model)
@@ -643,7 +646,7 @@ def build_llama_stages(cfg: LlamaConfig, n_stages: int, only: Optional[Sequence[
                 mods.append(LlamaEmbedding(cfg))
             mods += _modules_for_range(cfg, first, last, parts_per_layer)
             if i == n_stages - 1:
-                mods.append(LlamaHead(cfg))
+                mods.append(LlamaHead(cfg, fused_loss=fused_head_loss))
             tupled = any(isinstance(m, (LlamaMLPUpBlock, LlamaMLPDownBlock)) for m in mods)
             stage = (LlamaTupleStage if tupled else LlamaStage)(*mods).to(dtype)
         init_llama_(stage, cfg.init_std, seed + i)

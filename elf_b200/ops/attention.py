@@ -2,11 +2,13 @@
 
 ``attention(q, k, v)`` takes ``q [B, S, Hq, D]`` and ``k, v [B, S, Hkv, D]`` (any strides with a
 contiguous head dim — e.g. slices of one fused QKV projection) and returns ``[B, S, Hq, D]``.
-Back ends: ``torch.nn.functional.scaled_dot_product_attention`` by default (a library call, also
-what the reference's model zoo uses, ``benchmarks/models/simple.py:14-25,381-386``); with
-``ELF_B200_ATTENTION=native`` the packed entry point runs this package's tcgen05 forward and
-backward kernels (``attention_native.py``), which are correct but slower than the library's on
-the benchmarked shapes.
+Back ends: on CUDA with bf16, head dimension 128 and a sequence length that is a multiple of 128
+the packed entry point runs this package's tcgen05 forward kernel (``attention_native.py``); its
+backward is the library's fused kernel fed with our output and log-sum-exp unless
+``ELF_B200_ATTENTION_BACKWARD=native`` selects the own backward kernels.  Everything else, and
+``ELF_B200_ATTENTION=library``, goes through ``torch.nn.functional.scaled_dot_product_attention``
+(a library call, also what the reference's model zoo uses,
+``benchmarks/models/simple.py:14-25,381-386``).
 """
 
 from __future__ import annotations

@@ -326,6 +326,7 @@ def test_llama_layer_with_native_attention(dev):
     layer = init_llama_(LlamaDecoderLayer(cfg).to(dev).to(torch.bfloat16), 0.05, seed=1)
     x = torch.randn(2, 256, 512, device=dev, dtype=torch.bfloat16)
     results = []
+    default_mode = A._MODE
     for mode in ("library", "native"):
         A.set_mode(mode)
         try:
@@ -334,7 +335,7 @@ def test_llama_layer_with_native_attention(dev):
             y.float().square().mean().backward()
             results.append((y.detach(), xi.grad.detach()))
         finally:
-            A.set_mode("library")
+            A.set_mode(default_mode)
     assert rel_err(results[1][0], results[0][0]) < 1e-2
     assert rel_err(results[1][1], results[0][1]) < 2e-2
 
