@@ -36,6 +36,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from ..utils import stream_debug as _sd
 from ..utils.metadata import TensorMetadata
 
 __all__ = ["Channel", "ChannelTable", "edge_list"]
@@ -277,7 +278,10 @@ class _CopyLink:
         seq = self.sent
         slot = (seq - 1) % self.depth
         cur = torch.cuda.current_stream(self.device)
+        _sd.note_write(payload, cur, "stage output")
         self.stream.wait_stream(cur)  # the payload's producer kernels
+        _sd.note_sync(self.stream, cur)
+        _sd.check_read(payload, self.stream, "copy into the consumer's ring")
         with torch.cuda.stream(self.stream):
             if seq > self.depth:  # the consumer must have copied out the message this one overwrites
                 self.ext.p2p_wait(self.flags, 1, seq - self.depth, self.timeout_ms, self.status, self.where)

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..scheduling.scheduling import Operation, OperationType, OpOptions
+from ..utils import stream_debug as _sd
 from ..utils.timers import Timer
 from .block import PipelineBlock
 from .offload import OffloadManager, OffloadToCPU, PinnedHostTensorPool
@@ -141,6 +142,10 @@ class Engine:
             y = block.forward(op.mb_id, **op.options)
         if y is not None:
             self._results[op.mb_id] = [t.detach() if isinstance(t, torch.Tensor) else t for t in y]
+            if self.on_cuda and _sd.enabled():
+                for t in self._results[op.mb_id]:
+                    if isinstance(t, torch.Tensor):
+                        _sd.note_write(t, torch.cuda.current_stream(self.device), "output of the last stage")
 
     def _backward_inputs(self, block: PipelineBlock, op: Operation):
         block.backward_inputs(op.mb_id, **op.options)
@@ -210,11 +215,14 @@ class Engine:
         if self.outputs in (None, False, "none"):
             self._results[mb] = None
         elif self.outputs == "cpu" and self.on_cuda:
-            self.result_stream.wait_stream(torch.cuda.current_stream(self.device))
+            cur = torch.cuda.current_stream(self.device)
+            self.result_stream.wait_stream(cur)
+            _sd.note_sync(self.result_stream, cur)
             with torch.cuda.stream(self.result_stream), torch.no_grad():
                 moved = []
                 for t in self._results[mb]:
                     if isinstance(t, torch.Tensor):
+                        _sd.check_read(t, self.result_stream, "copy of a result to the host")
                         t.record_stream(self.result_stream)
                         t = t.to("cpu", non_blocking=True)
                     moved.append(t)

@@ -23,6 +23,8 @@ from weakref import ref
 
 import torch
 
+from ..utils import stream_debug as _sd
+
 from ..ops import _ext
 
 logger = logging.getLogger("offload")
@@ -168,7 +170,11 @@ class OffloadToCPU:
         flat = torch.as_strided(src.detach(), (span,), (1,), 0)
         mgr = self._mgr
         if mgr.on_cuda and src.is_cuda:
-            mgr.d2h_stream.wait_stream(torch.cuda.current_stream(src.device))
+            cur = torch.cuda.current_stream(src.device)
+            _sd.note_write(src, cur, "activation saved for backward")
+            mgr.d2h_stream.wait_stream(cur)
+            _sd.note_sync(mgr.d2h_stream, cur)
+            _sd.check_read(src, mgr.d2h_stream, "offload copy to the host")
             with torch.cuda.stream(mgr.d2h_stream):
                 host.copy_(flat, non_blocking=True)
                 src.record_stream(mgr.d2h_stream)  # keep the device memory alive until copied
@@ -195,6 +201,9 @@ class OffloadToCPU:
         ev = self._h2d_done.get(key)
         if ev is not None:
             torch.cuda.current_stream(rec["device"]).wait_event(ev)
+            _sd.note_sync(torch.cuda.current_stream(rec["device"]), self._mgr.h2d_stream)
+        if base.is_cuda:
+            _sd.check_read(base, torch.cuda.current_stream(rec["device"]), "prefetched activation used by the backward")
         return torch.as_strided(base, rec["size"], rec["stride"], rec["offset"])
 
     # ------------------------------------------------------------------ prefetch / release
@@ -217,6 +226,7 @@ class OffloadToCPU:
                 mgr.h2d_stream.wait_event(ev)
             with torch.cuda.stream(mgr.h2d_stream):
                 buf.copy_(host, non_blocking=True)
+                _sd.note_write(buf, mgr.h2d_stream, "prefetch copy from the host")
                 done = torch.cuda.Event()
                 done.record(mgr.h2d_stream)
             self._on_device[key] = buf

@@ -205,3 +205,33 @@ def test_measured_cost_model_on_the_device(dev):
     mode = choose_llama_cut(cfg, 4, placement, cm)
     costs = llama_stage_costs(cfg, 4, placement, mode, cm)
     assert abs(sum(costs) - (cfg.n_layers + cm.head + cm.embed)) < 1e-6
+
+
+def test_stream_order_checker_accepts_the_runtime_and_catches_a_missing_wait(dev):
+    """With the stream-order debug mode on, a step that offloads activations, prefetches them and
+    copies its outputs to the host raises nothing (every hand-off between streams is preceded by a
+    wait); a hand-off made without the wait is reported."""
+    from elf_b200.registry import SCHEDULERS
+    from elf_b200.scheduling.ilp import RematScheduler
+    from elf_b200.utils import stream_debug as sd
+
+    sd.enable(True)
+    try:
+        placement, nmb = [0, 0], 4
+        sched = RematScheduler(SCHEDULERS["1f1b"], _solution(2, nmb, offload=[(0, 0), (0, 2), (1, 1), (1, 3)]))
+        pipe, ref, GPT, ids, tgt = _gpt(dev, sched, placement)
+        pipe.engine.outputs = "cpu"
+        out, loss = pipe(ids, tgt, GPT.loss_fn, split_size=1)
+        torch.cuda.synchronize()
+        assert len(out) == nmb and out[0].device.type == "cpu"
+        # the same kind of hand-off without its wait
+        side = torch.cuda.Stream(dev)
+        buf = torch.ones(1 << 20, device=dev)
+        sd.note_write(buf, torch.cuda.current_stream(dev), "compute result")
+        with pytest.raises(sd.StreamOrderError):
+            sd.check_read(buf, side, "side-stream copy")
+        side.wait_stream(torch.cuda.current_stream(dev))
+        sd.note_sync(side, torch.cuda.current_stream(dev))
+        sd.check_read(buf, side, "side-stream copy")
+    finally:
+        sd.enable(False)
