@@ -87,6 +87,7 @@ def run_ours(args):
         from elf_b200.models.llama_costs import measure_cost_model
 
         cost_model = measure_cost_model(cfg, device, mb_size=args.mb_size)
+        cost_model.micro_batches = args.nmb  # lets the cut allow for the pipeline's fill (deep ranks start late once per step)
     if pp == 1 or args.whole_layers:
         split_layers = False
     elif args.split_thirds:

@@ -336,7 +336,7 @@ THIRD_SHARES = (ATTENTION_SHARE, 0.55, 0.25)
 
 
 def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence[int]] = None, head_units: float = 0.0, attention_share: float = ATTENTION_SHARE,
-                      shares: Optional[Sequence[float]] = None, embed_units: float = 0.0):
+                      shares: Optional[Sequence[float]] = None, embed_units: float = 0.0, fill_share: float = 0.0):
     """Split the 2·n_layers half-layers (attention half, MLP half, attention half, ...) into
     ``n_stages`` contiguous ranges so that the busiest *rank* has as little work as possible.
 
@@ -350,7 +350,11 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     ``shares`` generalises the unit: a layer is cut into ``len(shares)`` consecutive parts of those
     relative costs (``THIRD_SHARES`` = attention, gate/up + SwiGLU, down projection) and the
     ranges index those parts.  ``embed_units`` is the cost of the embedding (in layers), carried
-    by the first stage the way ``head_units`` is carried by the last."""
+    by the first stage the way ``head_units`` is carried by the last.  ``fill_share`` (V placements):
+    share of a stage's time that is its forward pass; rank ``r`` cannot start before the first
+    micro-batch has gone through the ``r`` front stages before it, so that much is counted against
+    its budget and ranks deep in the pipeline get correspondingly less work (all ranks then finish
+    together instead of the last starter finishing last)."""
     shares = tuple(shares) if shares is not None else (attention_share, 1.0 - attention_share)
     k = len(shares)
     n_blocks = k * n_layers
@@ -376,6 +380,20 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     n_ranks = len(set(placement))
     is_v = n_stages == 2 * n_ranks and placement == list(range(n_ranks)) + list(range(n_ranks - 1, -1, -1))
     bounds = _v_bottleneck_bounds(prefix, n_ranks, head_units) if is_v else None
+    if is_v and bounds is not None and fill_share > 0.0:
+        # the offsets depend on the cut (time of the front stages before each rank): two rounds settle it
+        for _ in range(3):
+            fronts = [prefix[bounds[s + 1]] - prefix[bounds[s]] for s in range(n_ranks)]
+            offsets, acc = [], 0.0
+            for r in range(n_ranks):
+                offsets.append(fill_share * acc)
+                acc += fronts[r]
+            again = _v_bottleneck_bounds(prefix, n_ranks, head_units, rank_offsets=offsets)
+            if again is None or again == bounds:
+                break
+            bounds = again
+        ranges = [(bounds[s], bounds[s + 1]) for s in range(n_stages)]
+        return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
     if bounds is None:
         # proportional start: stage s ends where the running cost reaches its share of the total
         # (the head's units count towards the last stages' share)
@@ -410,7 +428,7 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
 
 
-def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, window: float = 1.0) -> Optional[List[int]]:
+def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, window: float = 1.0, rank_offsets: Optional[Sequence[float]] = None) -> Optional[List[int]]:
     """Exact partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th range from
     the front and the r-th range from the back (the last one also carries the head).  First the
     smallest possible bottleneck T (busiest rank) is found by bisection; then, among the
@@ -422,6 +440,9 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
     n, p = len(prefix) - 1, n_ranks
     if n < 2 * p:
         return None
+    # rank_offsets[r]: time rank r cannot use anyway (it starts r hops after rank 0), counted
+    # against its budget so that late starters get less work and all ranks finish together
+    off = list(rank_offsets) if rank_offsets is not None else [0.0] * p
 
     def sweep(T, want_bounds, window=None):
         # states[(i, j)] = (sum of squared stage costs so far, previous state); with a window only
@@ -435,10 +456,10 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
             for (i, j), (sq, _) in states.items():
                 for i2 in range(i + 1, j):
                     front = prefix[i2] - prefix[i]
-                    budget = T - extra - front
+                    budget = T - off[r] - extra - front
                     if budget < -1e-12:
                         break
-                    if window is not None and (front < T / 2 - window or front > T / 2 + window):
+                    if window is not None and (front < (T - off[r]) / 2 - window or front > (T - off[r]) / 2 + window):
                         continue
                     lo = i2 if r == p - 1 else i2 + left_after  # the last rank's back range closes the gap exactly
                     hi = i2 if r == p - 1 else j - 1
@@ -448,7 +469,7 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
                         back = prefix[j] - prefix[j2]
                         if back > budget + 1e-12:
                             break
-                        if window is not None and back + extra < T / 2 - window:
+                        if window is not None and back + extra < (T - off[r]) / 2 - window:
                             continue
                         cand = sq + front * front + (back + extra) * (back + extra)
                         key = (i2, j2)
@@ -483,7 +504,7 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
             nxt = {}
             for i, j in reach.items():
                 for i2 in range(i + 1, j):
-                    budget = T - extra - (prefix[i2] - prefix[i])
+                    budget = T - off[r] - extra - (prefix[i2] - prefix[i])
                     if budget < -1e-12:
                         break
                     if r == p - 1:
@@ -505,7 +526,7 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
             reach = nxt
         return any(j == i for i, j in reach.items())
 
-    lo, hi = 0.0, prefix[-1] + head_units
+    lo, hi = 0.0, prefix[-1] + head_units + max(off)
     if not reachable(hi):
         return None
     for _ in range(30):
@@ -552,6 +573,7 @@ def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers, cost
     """(ranges, parts per layer, costs) for ``split_layers`` = False, True / "halves" or "thirds".
     ``cost_model`` (``elf_b200.models.llama_costs.LlamaCostModel``) replaces the built-in constants
     for the parts of a layer, the head and the embedding - typically measured on the device."""
+    fill = 0.0
     if cost_model is None:
         head = head_cost_in_layers(cfg) if placement is not None else 0.0
         embed, halves, thirds = 0.0, None, THIRD_SHARES
@@ -559,11 +581,14 @@ def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers, cost
         head = cost_model.head if placement is not None else 0.0
         embed = cost_model.embed if placement is not None else 0.0
         halves, thirds = cost_model.shares(2), cost_model.shares(3)
+        # a rank's wait for the first micro-batch happens once per step, its load once per micro-batch
+        nmb = getattr(cost_model, "micro_batches", None)
+        fill = float(cost_model.fbw[0]) / nmb if nmb else 0.0
     if split_layers in (True, "halves"):
-        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=halves, embed_units=embed)
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=halves, embed_units=embed, fill_share=fill)
         return ranges, 2, costs
     if split_layers == "thirds":
-        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=thirds, embed_units=embed)
+        ranges, costs = half_layer_ranges(cfg.n_layers, n_stages, placement, head, shares=thirds, embed_units=embed, fill_share=fill)
         return ranges, 3, costs
     assert not split_layers, f"split_layers must be False, True, 'halves' or 'thirds', got {split_layers!r}"
     counts = layers_per_stage(cfg.n_layers, n_stages, placement, head)

@@ -31,6 +31,8 @@ class LlamaCostModel:
     ``embed``       embedding lookup and its gradient
     ``layer_ms``    milliseconds of one layer per micro-batch when measured, else ``None``
     ``fbw``         share of a layer's time spent in forward / input-gradient / weight-gradient passes
+    ``micro_batches``  when set, the cut on a V placement is skewed for the pipeline's fill: rank ``r``
+                    starts ``r`` forward stages late once per step, so it gets that much less work
     """
 
     attention: float
@@ -41,6 +43,7 @@ class LlamaCostModel:
     layer_ms: Optional[float] = None
     fbw: Tuple[float, float, float] = (0.31, 0.44, 0.25)
     source: str = "analytic"
+    micro_batches: Optional[int] = None
 
     @property
     def mlp(self) -> float:

@@ -1,6 +1,7 @@
 """Stage cuts of the Llama-style decoder: cost models, where the boundaries fall, which
 granularity is chosen."""
 
+import pytest
 import torch
 
 from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, choose_llama_cut, llama_stage_costs, llama_stage_ranges, llama_stage_signatures
@@ -63,3 +64,22 @@ def test_cut_granularity_follows_the_balance():
         out = y if isinstance(y, tuple) else (y,)
         assert len(sig.outputs) == len(out)
     assert out[0].shape == (2, small.seq_len, small.vocab)
+
+
+def test_cut_allows_for_the_pipeline_fill():
+    """With the number of micro-batches known, ranks deep in a V pipeline (which start late, once per
+    step) get less work: what is minimised is load + time lost waiting for the first micro-batch."""
+    pl = v(8)
+    base = LlamaCostModel(0.32, 0.45, 0.23, head=1.8, embed=0.04, fbw=(0.34, 0.42, 0.24))
+    skew = LlamaCostModel(0.32, 0.45, 0.23, head=1.8, embed=0.04, fbw=(0.34, 0.42, 0.24), micro_batches=16)
+
+    def finish(model):
+        costs = llama_stage_costs(CFG, 16, pl, "thirds", model)
+        ld = loads(costs, pl)
+        fill = [0.34 / 16 * sum(costs[:r]) for r in range(8)]
+        return max(a + b for a, b in zip(ld, fill)), ld
+
+    t0, ld0 = finish(base)
+    t1, ld1 = finish(skew)
+    assert t1 < t0
+    assert ld1[0] > ld1[-1] and sum(ld1) == pytest.approx(sum(ld0))
