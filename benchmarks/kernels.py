@@ -242,9 +242,13 @@ def one_fused(args):
         fused.rms_norm(x, w, 1e-5).float().sum().backward()
         fused.swiglu(gu).float().sum().backward()
         fused.cross_entropy(logits.clone(), tgt).backward()
-        fused.embedding(table, ids).float().sum().backward()
+        fused.embedding(table, ids, into_grad=True).float().sum().backward()
         fused.rope_(qkv, cos, sin, 40, 128, T)
-        _ext.get().adamw(p, gr, master, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+        ext = _ext.get()
+        ext.residual_add(r, x.detach())
+        q4 = qkv.view(1, T, 48, 128)
+        ext.pack_qkv_grad(q4[:, :, :32], q4[:, :, 32:40], q4[:, :, 40:], cos, sin)
+        ext.adamw(p, gr, master, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
     torch.cuda.synchronize()
     print("done fused")
 

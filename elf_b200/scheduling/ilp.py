@@ -310,6 +310,29 @@ def profile(stages: List[torch.nn.Module], samples: List[Sequence[torch.Tensor]]
     return out
 
 
+def _drop_fake_caches(model: torch.nn.Module) -> None:
+    """Modules may cache tensors they compute on first use (rotary tables, masks).  A cache filled
+    during the shape-propagation pass holds fake tensors; left in place, later real forwards would
+    compute on them and hand fake outputs to the transport.  Reset such attributes to ``None``."""
+    from torch._subclasses.fake_tensor import FakeTensor
+
+    def is_fake(v) -> bool:
+        if isinstance(v, FakeTensor):
+            return True
+        if isinstance(v, (tuple, list)):
+            return any(is_fake(x) for x in v)
+        if isinstance(v, dict):
+            return any(is_fake(x) for x in v.values())
+        return False
+
+    for m in model.modules():
+        for name, value in list(vars(m).items()):
+            if name.startswith("_parameters") or name in ("_buffers", "_modules"):
+                continue
+            if is_fake(value):
+                setattr(m, name, None)
+
+
 def propagate_sample(block_models: Dict[int, torch.nn.Module], placement, sample, pp_group, to_global: Callable[[int], int] = lambda r: r, my_rank: Optional[int] = None):
     """Input metadata of every local block, found by running the blocks on ``meta`` copies
     of their inputs stage after stage; at rank boundaries only the shapes travel (as a
@@ -345,6 +368,7 @@ def propagate_sample(block_models: Dict[int, torch.nn.Module], placement, sample
             for m in model.modules():
                 if isinstance(m, LayerDW):
                     m.clear()
+            _drop_fake_caches(model)
         elif prev == my_rank and block_id:
             dist.send_object_list([[(m.shape, m.dtype) for m in out_meta]], dst=to_global(owner), group=pp_group)
     return metas

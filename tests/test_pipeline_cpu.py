@@ -237,3 +237,31 @@ def test_thirds_cut_with_untagged_channels():
         run_ranks(_split_layer_worker, 2, "thirds")
     finally:
         os.environ.pop("ELF_B200_P2P_STRICT")
+
+
+def _budget_worker(rank, world):
+    """Llama stages (which cache rotary tables on first use) on two ranks with a memory budget: the
+    shape-propagation pass of the stage profiler must leave nothing fake behind in the modules."""
+    from elf_b200 import Pipeline, Placement
+    from elf_b200.models.llama import LLAMA_CONFIGS, build_llama_stages, llama_loss_fn
+
+    cfg = LLAMA_CONFIGS["llama-tiny"]
+    placement = Placement.default("zbv", world)
+    mine = placement.get_ids(rank)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g)
+    losses = []
+    for budget in (None, 1e6):
+        stages = build_llama_stages(cfg, len(placement), only=mine, device="cpu", dtype=torch.float32, seed=1, placement=list(placement))
+        pipe = Pipeline([stages[i] for i in mine], tok[:1, :-1].contiguous(), partitioner=False, scheduler="zbv", placement=list(placement), outputs="none", memory_budget=budget)
+        _, loss = pipe(tok[:, :-1].contiguous(), tok[:, 1:].contiguous(), llama_loss_fn, split_size=1)
+        losses.append(loss)
+        if budget is not None:
+            assert len(pipe.get_profiling_statistics()) == len(placement)
+        pipe.clear()
+    if losses[0] is not None:
+        torch.testing.assert_close(losses[0], losses[1], atol=1e-5, rtol=1e-5)
+
+
+def test_memory_budget_on_two_ranks_with_llama_stages():
+    run_ranks(_budget_worker, 2, timeout=150.0)
