@@ -261,13 +261,18 @@ def run_reference(args) -> None:
             fence()
             e2e_ms = max_ranks(start.elapsed_time(end))
             tokens = args.dp * batch * c["seq_len"] * args.steps
-            io_rank = placement[0] == rank % pp or placement[-1] == rank % pp
+            # bytes of the whole job per step: every rank copies its batch of token ids to its GPU
+            # (only the ranks hosting the first and the last stage read them), the rank that owns
+            # the loss reads it back; summed over ranks so that the line does not depend on which
+            # rank prints it
+            io = torch.tensor([int(host[0].numel() * host[0].element_size()), 4 if placement[-1] == rank % pp else 0], dtype=torch.float64, device=device)
+            dist.all_reduce(io, op=dist.ReduceOp.SUM)
             e2e = {
                 "value": tokens / (e2e_ms / 1e3),
                 "unit": "tokens/s",
                 "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": int(host[0].numel() * host[0].element_size()) if io_rank else 0,
-                "d2h_bytes_per_step": 4 if placement[-1] == rank % pp else 0,
+                "h2d_bytes_per_step": int(io[0].item()),
+                "d2h_bytes_per_step": int(io[1].item()),
             }
     except torch.cuda.OutOfMemoryError as exc:
         return _unavailable(f"reference ran out of GPU memory on this configuration: {str(exc)[:120]}")

@@ -302,6 +302,13 @@ def run_ours(args):
 
 def main():
     args = parse_args()
+    dump_after = os.environ.get("ELF_B200_DUMP_STACKS_AFTER")
+    if dump_after:  # debugging aid: write every thread's Python stack to a file after so many seconds, then exit
+        import faulthandler
+
+        path = os.path.join(os.environ.get("ELF_B200_DUMP_DIR", "."), f"stacks_rank{os.environ.get('RANK', '0')}.txt")
+        main._stack_file = open(path, "w")
+        faulthandler.dump_traceback_later(float(dump_after), exit=True, file=main._stack_file)
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 

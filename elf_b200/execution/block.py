@@ -94,6 +94,8 @@ class Variable:
 
 
 class PipelineBlock:
+    _step_counter = 0  # bumped by the pipeline at the start of every step (see all_reduce_param_grads)
+
     def __init__(self, model, id_, placement, signature, pp_group=None, dp_group=None, channels=None, device=None, rank=None):
         """``placement`` holds pipeline-local ranks; ``channels`` is this rank's
         ``ChannelTable`` (``None`` for a single-rank pipeline)."""
@@ -339,10 +341,26 @@ class PipelineBlock:
         if self.dp_group is None or dist.get_world_size(self.dp_group) == 1:
             return
         world = dist.get_world_size(self.dp_group)
-        grads = [p.grad for _, p in sorted(self.model.named_parameters(), key=lambda kv: kv[0]) if p.grad is not None]
+        avg_ok = dist.get_backend(self.dp_group) == "nccl"
+        # parameters living in a flat buffer (the fused optimizer's): reduce the buffer in place, one
+        # collective, no gather / scatter copies.  A buffer shared by several stages of this rank is
+        # reduced once per step, by whichever stage gets here first (every W pass of the step is
+        # done by then: the all-reduce operations close the schedule).
+        loose = []
+        for _, p in sorted(self.model.named_parameters(), key=lambda kv: kv[0]):
+            group = getattr(p, "_elf_flat_group", None)
+            if group is None or group.grad_dtype != p.dtype or p.grad is None or p.grad.data_ptr() != group.grad_view(group.params.index(p)).data_ptr():
+                if p.grad is not None:
+                    loose.append(p.grad)
+                continue
+            if getattr(group, "_reduced_in_step", None) == PipelineBlock._step_counter:
+                continue
+            group._reduced_in_step = PipelineBlock._step_counter
+            work = dist.all_reduce(group.flat_grad, op=dist.ReduceOp.AVG if avg_ok else dist.ReduceOp.SUM, group=self.dp_group, async_op=True)
+            self._pending_reduce.append((work, group.flat_grad, [], 1.0 if avg_ok else 1.0 / world))
+        grads = loose
         if not grads:
             return
-        avg_ok = dist.get_backend(self.dp_group) == "nccl"
         by_dtype: Dict[torch.dtype, List[torch.Tensor]] = {}
         for g in grads:
             by_dtype.setdefault(g.dtype, []).append(g)
@@ -362,6 +380,10 @@ class PipelineBlock:
     def wait_grad_sync(self) -> None:
         for work, flat, bucket, factor in self._pending_reduce:
             work.wait()
+            if not bucket:  # a flat gradient buffer reduced in place
+                if factor != 1.0:
+                    flat.mul_(factor)
+                continue
             offset = 0
             for g in bucket:
                 n = g.numel()

@@ -303,6 +303,7 @@ class Pipeline:
         if regenerate:
             self._generate_schedule(nmb, sched, self.cfg.comm_scheduler, mb_sizes)
             self.last_nmb = nmb if scheduler is None else 0
+        PipelineBlock._step_counter += 1
         for block in self.blocks:
             for layer in block.dw_layers():
                 layer.clear()
