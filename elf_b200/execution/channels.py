@@ -190,20 +190,12 @@ class Channel:
         self._posted.clear()
         self._deferred.clear()
 
-    def switch_to_copy(self, depth: int = 4, timeout_ms: float = 60000.0) -> bool:
-        """Collective over the two ranks of this channel: agree on the slot size (the largest
-        message either end has seen), allocate and map the ring, and route all later traffic
-        through it.  Returns whether the channel switched (it stays on NCCL if it has carried
-        no message yet).  Call between steps, with nothing of this channel in flight."""
-        assert not self._posted and not self._deferred, "switch_to_copy with receives in flight"
+    def attach_link(self, link: "_CopyLink") -> None:
+        """Route all later traffic of this channel through ``link`` (see ``ChannelTable.upgrade_to_copy``).
+        Called between steps, with nothing of this channel in flight."""
+        assert not self._posted and not self._deferred, "transport switched with receives in flight"
         self.reap_sends(block=True)
-        size = torch.tensor([self.max_message_bytes], dtype=torch.int64, device=self.device)
-        dist.all_reduce(size, op=dist.ReduceOp.MAX, group=self.group)
-        slot_bytes = int(size.item())
-        if slot_bytes == 0:
-            return False
-        self.link = _CopyLink(self, (slot_bytes + 255) // 256 * 256, depth, timeout_ms)
-        return True
+        self.link = link
 
     def end_step(self) -> None:
         """Forget receives that were posted but not consumed in the step that just ended."""
@@ -223,8 +215,9 @@ class Channel:
 class _CopyLink:
     """One end of a channel on the copy transport.
 
-    Both ranks allocate the same symmetric buffer: ``depth`` slots of ``slot_bytes`` followed by
-    a flag area.  The consumer's copy holds the ring; flag 0 of the consumer = sequence number
+    Every rank of the pipeline holds one symmetric arena with a region per channel at the same
+    offset: ``depth`` slots of ``slot_bytes`` followed by a flag area.  The consumer's copy of the
+    region holds the ring; flag 0 of the consumer = sequence number
     of the newest message that has landed, flag 1 of the producer = newest message the consumer
     has copied out (so slot reuse never overtakes the consumer).  Messages are numbered 1, 2, ...
     for the life of the channel and must be taken in the order they were posted, which is the
@@ -232,9 +225,10 @@ class _CopyLink:
 
     FLAG_BYTES = 256
 
-    def __init__(self, channel: "Channel", slot_bytes: int, depth: int, timeout_ms: float):
-        import torch.distributed._symmetric_memory as symm_mem
-
+    def __init__(self, channel: "Channel", arena: torch.Tensor, peer_arena: torch.Tensor, peer_base_addr: int, offset: int, slot_bytes: int, depth: int, timeout_ms: float):
+        """``arena`` is this rank's symmetric buffer, ``peer_arena`` the peer's copy of it as mapped
+        here (``peer_base_addr`` its device address); the channel's region starts ``offset`` bytes
+        in on both: ``depth`` slots of ``slot_bytes``, then ``FLAG_BYTES`` of flags."""
         from ..ops import _ext
         from ..ops import gemm as _gemm
 
@@ -245,17 +239,11 @@ class _CopyLink:
         self.channel = channel
         self.device = channel.device
         self.depth, self.slot_bytes, self.timeout_ms = depth, slot_bytes, timeout_ms
-        total = depth * slot_bytes + self.FLAG_BYTES
-        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
-        self.handle = symm_mem.rendezvous(self.buf, group=channel.group.group_name)
-        self.buf.zero_()
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group=channel.group)  # nobody raises a flag before both rings are zeroed
-        me = self.handle.rank
-        peer = 1 - me
-        self.flags = self.buf[depth * slot_bytes :].view(torch.int32)
-        self.peer_buf = self.handle.get_buffer(peer, (total,), torch.uint8)
-        self.peer_flag_addr = int(self.handle.buffer_ptrs[peer]) + depth * slot_bytes
+        ring = depth * slot_bytes
+        self.buf = arena[offset : offset + ring]
+        self.flags = arena[offset + ring : offset + ring + self.FLAG_BYTES].view(torch.int32)
+        self.peer_buf = peer_arena[offset : offset + ring]
+        self.peer_flag_addr = peer_base_addr + offset + ring
         self.status = _gemm.status(self.device)
         self.stream = torch.cuda.Stream(self.device)  # producer side: copies run here, behind the compute stream's event
         self.sent = 0  # producer: messages sent
@@ -331,6 +319,8 @@ class ChannelTable:
                 width = max(1, sum(1 for src in signatures[b].sources if src == a))
                 edges += [(a, b, k) for k in range(width)]
         n = 2 * len(edges)
+        self.pp_group, self.n_channel_ids, self.device = pp_group, n, device
+        self._arena = None
         self._order: List[Tuple[int, int, str, int]] = []  # this rank's channels in creation order (the same relative order on both ends)
         self.transport = "nccl" if backend == "nccl" else backend
         for replica in range(dp if dedicated_groups else 1):
@@ -351,7 +341,9 @@ class ChannelTable:
                         continue
                     src, dst = (a, b) if direction == "fwd" else (b, a)
                     peer_local = rb if local_rank == ra else ra
-                    self.channels[(src, dst, direction, k)] = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
+                    ch = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
+                    ch.peer_local = peer_local  # the peer's rank inside the pipeline group
+                    self.channels[(src, dst, direction, k)] = ch
                     self._order.append((src, dst, direction, k))
 
     def get(self, src_block: int, dst_block: int, direction: str, k: int = 0) -> Channel:
@@ -359,20 +351,61 @@ class ChannelTable:
         return self.channels[(src_block, dst_block, direction, k)]
 
     def upgrade_to_copy(self, depth: int = 4, timeout_ms: float = 60000.0) -> int:
-        """Switch every channel that has carried traffic to the copy transport.  Every rank of
-        the job calls this at the same point between two steps; channels are visited in their
-        global creation order, and each switch only involves the channel's two ranks, so ranks
-        that share several channels meet them in the same order.  Returns how many of this rank's
-        channels switched."""
-        if not self.channels:
-            return 0  # a pipeline of one rank (data parallelism only) has no stage-to-stage traffic
-        if self.transport != "nccl" or not self._groups:
-            raise RuntimeError("the copy transport needs CUDA tensors and one NCCL group per channel")
+        """Switch every channel that has carried traffic to the copy transport.  Collective over the
+        pipeline group (every rank of the job calls it at the same point between two steps):
+
+        1. the ranks gather the largest message every channel has carried;
+        2. every rank allocates ONE symmetric arena laid out identically - a region per channel
+           (``depth`` slots + flags) - and the group maps the arenas in a single rendezvous.  (One
+           rendezvous per pipeline, entered by all of its ranks: the exchange behind it numbers its
+           rounds per process, so ranks that had rendezvoused pairwise a different number of times
+           would never meet.)
+        3. each channel end gets a link onto its region: the consumer's arena holds the ring, the
+           producer writes it through its mapping of that arena.
+
+        Returns how many of this rank's channels switched."""
+        if self.n_channel_ids == 0:  # nothing crosses ranks (data parallelism only)
+            return 0
+        if self.transport != "nccl":
+            raise RuntimeError("the copy transport needs CUDA tensors and NCCL process groups")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = self.pp_group
+        world = dist.get_world_size(group)
+        mine = {ch.index: int(ch.max_message_bytes) for ch in self.channels.values()}
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=group)
+        sizes = [0] * self.n_channel_ids
+        for part in gathered:
+            for idx, nbytes in part.items():
+                sizes[idx] = max(sizes[idx], nbytes)
+        offsets, total = {}, 0
+        for idx, nbytes in enumerate(sizes):
+            if nbytes == 0:
+                continue  # never used so far: stays on NCCL
+            slot = (nbytes + 255) // 256 * 256
+            offsets[idx] = (total, slot)
+            total += depth * slot + _CopyLink.FLAG_BYTES
+        if total == 0:
+            return 0
+        arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        handle = symm_mem.rendezvous(arena, group=group.group_name)
+        arena.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)  # nobody raises a flag before every arena is zeroed
+        self._arena = (arena, handle)
+        peers = {}
         switched = 0
         for key in self._order:
             ch = self.channels[key]
-            if ch.link is None and ch.switch_to_copy(depth, timeout_ms):
-                switched += 1
+            if ch.link is not None or ch.index not in offsets:
+                continue
+            off, slot = offsets[ch.index]
+            if ch.peer_local not in peers:
+                peers[ch.peer_local] = (handle.get_buffer(ch.peer_local, (total,), torch.uint8), int(handle.buffer_ptrs[ch.peer_local]))
+            peer_arena, peer_addr = peers[ch.peer_local]
+            ch.attach_link(_CopyLink(ch, arena, peer_arena, peer_addr, off, slot, depth, timeout_ms))
+            switched += 1
         self.transport = "copy"
         return switched
 

@@ -38,5 +38,11 @@ def test_pipeline_copy_engine_transport_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_pipeline_copy_engine_transport_four_gpus():
+    """Middle ranks have two neighbours: the arenas of all ranks are mapped in one rendezvous."""
+    launch("pp_copy", 4)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_pipeline_with_replicas_four_gpus():
     launch("pp_dp", 4)
