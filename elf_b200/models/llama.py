@@ -388,6 +388,9 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
             for r in range(n_ranks):
                 offsets.append(fill_share * acc)
                 acc += fronts[r]
+            # rank 0 runs the first forward and the last backward of a step and is never idle in
+            # between: what it is given beyond its share delays everybody, so a margin is kept free
+            offsets[0] = FIRST_RANK_MARGIN
             again = _v_bottleneck_bounds(prefix, n_ranks, head_units, rank_offsets=offsets)
             if again is None or again == bounds:
                 break
@@ -428,14 +431,23 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
 
 
+FIRST_RANK_MARGIN = 0.15  # layer units per micro-batch kept free on rank 0 of a V placement when the cut allows for the pipeline's fill
+BOTTLENECK_SLACK = 0.005  # partitions whose busiest rank is this close to the smallest possible one compete on the second criterion
+LOAD_WEIGHT = 8.0  # weight of squared rank loads against squared stage costs when choosing among partitions within the bottleneck
+
+
 def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, window: float = 1.0, rank_offsets: Optional[Sequence[float]] = None) -> Optional[List[int]]:
     """Exact partition for the V placement ``[0..p-1, p-1..0]``: rank r owns the r-th range from
     the front and the r-th range from the back (the last one also carries the head).  First the
     smallest possible bottleneck T (busiest rank) is found by bisection; then, among the
     partitions whose ranks all stay within T, the one with the smallest sum of squared *stage*
-    costs is taken, so that a rank's two stages are of similar size (a rank with a tiny front
-    stage and a huge back stage is balanced on paper but lengthens the pipeline's fill and
-    drain).  Both steps are a sweep over the ranks from the outside in over states
+    costs plus ``LOAD_WEIGHT`` times the sum of squared *rank* loads is taken.  The first term
+    keeps a rank's two stages of similar size (a rank with a tiny front stage and a huge back
+    stage is balanced on paper but lengthens the pipeline's fill and drain); the second keeps
+    every rank, not only the busiest, close to the mean, so that a part whose cost was measured
+    a few percent low does not turn a rank that sat just under T into the bottleneck (measured
+    on 8 B200s: rank 0, which carries the head, was given 4.53 layer units under a T of 4.54
+    and ran 4.8).  Both steps are a sweep over the ranks from the outside in over states
     (half-layers taken from the front, half-layers taken from the back)."""
     n, p = len(prefix) - 1, n_ranks
     if n < 2 * p:
@@ -471,7 +483,8 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
                             break
                         if window is not None and back + extra < (T - off[r]) / 2 - window:
                             continue
-                        cand = sq + front * front + (back + extra) * (back + extra)
+                        done = front + back + extra + off[r]
+                        cand = sq + front * front + (back + extra) * (back + extra) + LOAD_WEIGHT * done * done
                         key = (i2, j2)
                         if key not in nxt or cand < nxt[key][0] - 1e-12:
                             nxt[key] = (cand, (i, j))
@@ -535,7 +548,9 @@ def _v_bottleneck_bounds(prefix: List[float], n_ranks: int, head_units: float, w
             hi = mid
         else:
             lo = mid
-    T = hi * (1.0 + 1e-9) + 1e-9
+    # 0.5 % of slack over the smallest bottleneck: costs are measured to a few percent, and the
+    # second criterion chooses better among more partitions than the exact minimum admits
+    T = hi * (1.0 + BOTTLENECK_SLACK) + 1e-9
     while window < T:
         got = sweep(T, True, window)
         if got is not None:
@@ -598,10 +613,34 @@ def _stage_ranges(cfg: LlamaConfig, n_stages: int, placement, split_layers, cost
     return ranges, 2, [c + (head_last if i == n_stages - 1 else 0.0) + (embed if i == 0 else 0.0) for i, c in enumerate(counts)]
 
 
+def _simulated_step(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], mode, cost_model) -> float:
+    """Length (in layer units) of one ZB-V step over the stages ``mode`` cuts, as the timeline
+    simulator sees it: every stage's cost split into forward / input-gradient / weight-gradient
+    passes by ``cost_model.fbw``, rank 0's margin counted as work."""
+    from ..scheduling.scheduling import OperationType
+    from ..scheduling.schedulers import generate_zbv_schedule
+    from ..scheduling.simulator import simulate
+
+    costs = list(_stage_ranges(cfg, n_stages, list(placement), mode, cost_model)[2])
+    costs[0] += FIRST_RANK_MARGIN
+    fbw = tuple(float(x) for x in cost_model.fbw)
+    triples = [tuple(c * share for share in fbw) for c in costs]
+    which = {OperationType.FORWARD: 0, OperationType.BACKWARD_INPUTS: 1, OperationType.BACKWARD_PARAMS: 2}
+    n_ranks = len(set(placement))
+    sched = generate_zbv_schedule(list(placement), cost_model.micro_batches, cap="auto", cap_limit=6 * n_ranks, stage_costs=triples)
+    return simulate(sched, list(placement), lambda op: triples[op.block_id][which[op.op]] if op.op in which else 0.0).makespan
+
+
 def choose_llama_cut(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], cost_model=None, gain: float = 0.03):
     """``split_layers`` value to use for this placement: ``"thirds"`` (a third cut point per layer,
-    after SwiGLU; that boundary carries two tensors) when it lowers the busiest rank's load by more
-    than ``gain`` against cutting between attention and MLP halves only, else ``True``."""
+    after SwiGLU; that boundary carries two tensors) or ``True`` (cuts between attention and MLP
+    halves only).  On a V placement with a cost model that knows the number of micro-batches, both
+    cuts are laid out as ZB-V schedules and run through the timeline simulator, and thirds are taken
+    when their step is at least 0.5 % shorter.  (The busiest rank's load alone misjudges it: on 8
+    ranks with the Llama-3-8B shape the halves have the lighter busiest rank, 4.37 against 4.46
+    layer units, but leave rank 0, which nothing can wait for, 2 % more work and the simulated and
+    the measured step 4 % longer.)  Otherwise thirds are taken when they lower the busiest rank's
+    load by more than ``gain``."""
 
     def busiest(mode):
         costs = _stage_ranges(cfg, n_stages, list(placement), mode, cost_model)[2]
@@ -612,6 +651,10 @@ def choose_llama_cut(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], 
 
     if n_stages > 3 * cfg.n_layers:
         return True
+    n_ranks = len(set(placement))
+    is_v = n_stages == 2 * n_ranks and list(placement) == list(range(n_ranks)) + list(range(n_ranks - 1, -1, -1))
+    if is_v and n_ranks > 1 and cost_model is not None and getattr(cost_model, "micro_batches", None):
+        return "thirds" if _simulated_step(cfg, n_stages, placement, "thirds", cost_model) < 0.995 * _simulated_step(cfg, n_stages, placement, True, cost_model) else True
     return "thirds" if busiest("thirds") < (1.0 - gain) * busiest(True) else True
 
 

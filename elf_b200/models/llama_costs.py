@@ -74,95 +74,76 @@ def analytic_cost_model(cfg) -> LlamaCostModel:
     return LlamaCostModel(attention=0.2, mlp_up=0.55, mlp_down=0.25, head=head, embed=0.05)
 
 
-def _time_ms(fn, iters: int, device) -> float:
-    """Median device time of ``fn()`` over ``iters`` runs (CUDA events), after one untimed run."""
-    fn()
-    times = []
-    for _ in range(iters):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        b.synchronize()
-        times.append(a.elapsed_time(b))
-    times.sort()
-    return times[len(times) // 2]
+class _PartTimer:
+    """Runs one module on one micro-batch the way ``PipelineBlock`` runs a stage - the split-backward
+    layers stash their operands in the forward and the backward, and compute weight gradients in a
+    pass of their own - with a CUDA event between the passes."""
 
+    def __init__(self, module, make_input, loss=None):
+        from ..zb_utils import LayerDW
 
-def _fbw_of(module, make_input, device, iters: int, loss=None) -> Tuple[float, float, float]:
-    """(forward, input-gradient, weight-gradient) milliseconds of one module on one micro-batch,
-    run the way ``PipelineBlock`` runs a stage: the split-backward layers stash their operands in
-    the forward and the backward, and compute weight gradients in a pass of their own."""
-    from ..zb_utils import LayerDW
+        self.module, self.make_input, self.loss = module, make_input, loss
+        self.layers = [m for m in module.modules() if isinstance(m, LayerDW)]
+        self.marks = []
 
-    layers = [m for m in module.modules() if isinstance(m, LayerDW)]
-    state = {}
-
-    def clear():
-        for layer in layers:
+    def _clear(self):
+        for layer in self.layers:
             layer.clear()
 
-    def forward():
-        clear()
-        args = make_input()
-        state["in"] = args
-        out = module(*args)
-        state["out"] = out if not isinstance(out, tuple) else out
-        for layer in layers:
-            layer.move_last_computed("input", 0)
+    def run(self, timed: bool = True) -> None:
+        """Enqueue forward, input-gradient and weight-gradient pass; nothing waits for the device."""
 
-    def backward():
-        forward_out = state["out"]
-        if loss is not None:
-            loss(forward_out).backward()
+        def mark():
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+
+        e0 = mark()
+        self._clear()
+        out = self.module(*self.make_input())
+        for layer in self.layers:
+            layer.move_last_computed("input", 0)
+        e1 = mark()
+        if self.loss is not None:
+            self.loss(out).backward()
         else:
-            outs = forward_out if isinstance(forward_out, tuple) else (forward_out,)
+            outs = out if isinstance(out, tuple) else (out,)
             live = [o for o in outs if o.requires_grad]
             torch.autograd.backward(live, [torch.ones_like(o) for o in live])
-        for layer in layers:
+        for layer in self.layers:
             layer.move_last_computed("grad_output", 0)
-
-    def weights():
-        for layer in layers:
+        e2 = mark()
+        for layer in self.layers:
             slots = layer.ctx["grad_output"]
             if slots and slots[0] is not None:
                 layer.backward(0)
+        e3 = mark()
+        if timed:
+            self.marks.append((e0, e1, e2, e3))
 
-    # each pass is timed on fresh state produced by untimed runs of the passes before it
-    def timed(passes_before, the_pass):
-        def run():
-            for p in passes_before:
-                p()
-            torch.cuda.synchronize(device)
+    def result(self) -> Tuple[float, float, float]:
+        """Median (forward, input-gradient, weight-gradient) milliseconds of the timed runs; call
+        after a device synchronisation."""
 
-        times = []
-        for i in range(iters + 1):
-            run()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            the_pass()
-            b.record()
-            b.synchronize()
-            if i:
-                times.append(a.elapsed_time(b))
-        times.sort()
-        return times[len(times) // 2]
+        def median(k):
+            times = sorted(m[k].elapsed_time(m[k + 1]) for m in self.marks)
+            return times[len(times) // 2]
 
-    f = timed([], forward)
-    b = timed([forward], backward)
-    w = timed([forward, backward], weights) if layers else 0.0
-    clear()
-    state.clear()
-    for p in module.parameters():
-        p.grad = None
-    return f, b, w
+        out = (median(0), median(1), median(2) if self.layers else 0.0)
+        self._clear()
+        self.marks.clear()
+        for p in self.module.parameters():
+            p.grad = None
+        return out
 
 
-def measure_cost_model(cfg, device=None, dtype=torch.bfloat16, mb_size: int = 1, iters: int = 3, group=None) -> LlamaCostModel:
+def measure_cost_model(cfg, device=None, dtype=torch.bfloat16, mb_size: int = 1, iters: int = 10, group=None, burn_in_s: float = 0.7) -> LlamaCostModel:
     """Time one attention half, one gate/up part, one down part, the embedding and the head + loss
     of ``cfg`` on ``device`` (a CUDA device) for one micro-batch of ``mb_size`` sequences.  With
     ``group`` (a process group), rank 0's measurement is broadcast so that every rank cuts the model
-    identically.  Falls back to ``analytic_cost_model`` on CPU."""
+    identically.  Falls back to ``analytic_cost_model`` on CPU.  The parts are timed in turn, ``iters``
+    rounds, on a device kept busy (``burn_in_s`` seconds of work first, no idle gaps between the
+    timed passes), so the ratios are those of a power-limited GPU in the middle of a step."""
     import torch.distributed as dist
 
     from . import llama as L
@@ -184,17 +165,42 @@ def measure_cost_model(cfg, device=None, dtype=torch.bfloat16, mb_size: int = 1,
             replace_layer_with_layer_dw(m)
             return m
 
-        def hidden():
-            return (torch.randn(mb_size, s, d, device=device, dtype=dtype).requires_grad_(True),)
+        base = torch.randn(mb_size, s, d, device=device, dtype=dtype)
+        act = torch.randn(mb_size, s, cfg.ffn, device=device, dtype=dtype)
 
-        t = {}
-        t["attention"] = _fbw_of(build(L.LlamaAttentionBlock), hidden, device, iters)
-        t["mlp_up"] = _fbw_of(build(L.LlamaMLPUpBlock), hidden, device, iters)
-        t["mlp_down"] = _fbw_of(build(L.LlamaMLPDownBlock), lambda: (hidden()[0], torch.randn(mb_size, s, cfg.ffn, device=device, dtype=dtype).requires_grad_(True)), device, iters)
+        def hidden():
+            return (base.detach().requires_grad_(True),)
+
         ids = torch.randint(0, cfg.vocab, (mb_size, s), device=device)
-        t["embed"] = _fbw_of(build(L.LlamaEmbedding), lambda: (ids,), device, iters)
         target = torch.randint(0, cfg.vocab, (mb_size, s), device=device)
-        t["head"] = _fbw_of(build(L.LlamaHead), hidden, device, iters, loss=lambda logits: L.llama_loss_fn(logits, target, reduction="sum"))
+        jobs = {
+            "mlp_up": (build(L.LlamaMLPUpBlock), hidden, None),
+            "attention": (build(L.LlamaAttentionBlock), hidden, None),
+            "mlp_down": (build(L.LlamaMLPDownBlock), lambda: (hidden()[0], act.detach().requires_grad_(True)), None),
+            "embed": (build(L.LlamaEmbedding), lambda: (ids,), None),
+            "head": (build(L.LlamaHead), hidden, lambda logits: L.llama_loss_fn(logits, target, reduction="sum")),
+        }
+        timers = {name: _PartTimer(*job) for name, job in jobs.items()}
+        # Bring the device to the clock it sustains under load, then time the parts in turn,
+        # round after round, with no host synchronisation until the end: the GPU stays loaded the
+        # way it is inside a training step, and a drifting clock touches all parts alike.  (Timed
+        # one pass at a time between synchronisations, the device idles in between and runs each
+        # burst at a higher clock than its power limit lets it sustain; GEMM-heavy parts such as
+        # the head then look cheaper, relative to a layer, than they are in a pipeline.)
+        burner = timers["mlp_up"]
+        burner.run(timed=False)  # first call: one-time set-up of the kernels
+        burner.run()
+        torch.cuda.synchronize(device)
+        once = sum(burner.result())
+        for _ in range(min(2000, int(1e3 * burn_in_s / once)) if once > 0 else 0):
+            burner.run(timed=False)
+        for i in range(1 + iters):
+            for timer in timers.values():
+                timer.run(timed=i > 0)
+        torch.cuda.synchronize(device)
+        t = {name: timer.result() for name, timer in timers.items()}
+        del timers, burner
+        del jobs
         torch.cuda.empty_cache()
         total = {k: sum(v) for k, v in t.items()}
         layer = total["attention"] + total["mlp_up"] + total["mlp_down"]

@@ -464,7 +464,8 @@ class Pipeline:
         The last step must have run with per-operation timers (``ELF_TIMINGS=1``).  Meant for
         profile-guided schedules: feed the list to a cost-aware scheduler such as
         ``functools.partial(generate_zbv_schedule, cap="auto", stage_costs=costs)`` and install
-        it with ``set_scheduler``.  Stages without split backward report ``w = 0``."""
+        it with ``set_scheduler``.  Stages without split backward report ``w = 0``; the last stage's
+        ``b`` includes the loss and its backward."""
         import re
 
         events = (self.detailed_stats or {}).get("all_events") or {}
@@ -475,10 +476,17 @@ class Pipeline:
             m = re.match(r"(forward|backward_inputs|backward_params)\((\d+):\d+\)$", name)
             if m:
                 acc.setdefault(int(m.group(2)), {}).setdefault(m.group(1), []).append(float(secs))
+        # the loss and its backward run as operations of their own on the rank of the last stage:
+        # they count towards that stage's backward, or the rank looks lighter than it is
+        last = len(self.placement) - 1
+        timeline = (self.detailed_stats or {}).get("timeline") or {}
+        loss_f = [t1 - t0 for name, (t0, t1) in timeline.items() if name.split("#")[0] == "loss_forward"]
+        loss_b = [float(secs) for name, secs in events.items() if re.match(rf"backward\({last}:\d+\)$", name)]
+        loss_extra = (sum(loss_f) / len(loss_f) if loss_f else 0.0) + (sum(loss_b) / len(loss_b) if loss_b else 0.0)
         mine = {}
         for stage, kinds in acc.items():
             mean = lambda k: (sum(kinds[k]) / len(kinds[k])) if kinds.get(k) else 0.0
-            mine[stage] = (mean("forward"), mean("backward_inputs"), mean("backward_params"))
+            mine[stage] = (mean("forward"), mean("backward_inputs") + (loss_extra if stage == last else 0.0), mean("backward_params"))
         parts = [mine]
         if self.pp_group is not None and dist.is_initialized() and dist.get_world_size(self.pp_group) > 1:
             parts = [None] * dist.get_world_size(self.pp_group)

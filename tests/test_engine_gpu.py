@@ -196,7 +196,7 @@ def test_measured_cost_model_on_the_device(dev):
     from elf_b200.models.llama_costs import measure_cost_model
 
     cfg = LlamaConfig(n_layers=8, d_model=512, n_heads=4, n_kv_heads=2, ffn=1536, vocab=4096, seq_len=512, rope_theta=500000.0)
-    cm = measure_cost_model(cfg, dev, mb_size=2, iters=2)
+    cm = measure_cost_model(cfg, dev, mb_size=2, iters=2, burn_in_s=0.05)
     assert cm.source == "measured" and cm.layer_ms > 0
     assert abs(cm.attention + cm.mlp_up + cm.mlp_down - 1.0) < 1e-6
     assert min(cm.attention, cm.mlp_up, cm.mlp_down, cm.head, cm.embed) > 0
