@@ -36,6 +36,7 @@ from ..ops import _ext
 from ..ops import attention as _attn
 from ..ops import fused as _f
 from ..ops import gemm as _gemm
+from ..zb_utils import LayerDW, in_partial_replay
 
 __all__ = ["fused_apply", "attention_half", "mlp_half", "decoder_layer"]
 
@@ -59,7 +60,10 @@ def fused_apply(x: torch.Tensor, *linears) -> bool:
 
 
 def _norm_grad_target(w: torch.Tensor) -> torch.Tensor:
-    """Buffer the RMSNorm backward kernel accumulates the gain's gradient into."""
+    """Buffer the RMSNorm backward kernel accumulates the gain's gradient into (a throw-away one
+    while a partial backward replay refills the W-pass stashes: the gradient is in already)."""
+    if in_partial_replay():
+        return torch.zeros_like(w)
     target = getattr(w, "main_grad", None)
     if target is None:
         if w.grad is None:
@@ -244,6 +248,8 @@ class _DecoderLayer(torch.autograd.Function):
 
 # registered so that the partial backward replay treats these nodes like the per-linear ones
 _FUSED_FUNCTIONS = (_AttentionHalf, _MLPHalf, _DecoderLayer)
+for _fn in _FUSED_FUNCTIONS:
+    LayerDW._dx_function_registry[_fn] = _fn
 
 
 def attention_half(blk, x: torch.Tensor) -> torch.Tensor:

@@ -37,6 +37,7 @@ __all__ = [
     "replace_linear_with_linear_dw",
     "LayerDWTracer",
     "partial_dx_recomputation",
+    "in_partial_replay",
 ]
 
 
@@ -370,6 +371,16 @@ class LayerDWTracer(torch.fx.Tracer):
 # ---------------------------------------------------------------------------------------
 
 
+_replay_depth = 0
+
+
+def in_partial_replay() -> bool:
+    """True while ``partial_dx_recomputation`` runs: a backward node that also accumulates
+    parameter gradients as a side effect (a fused layer's norm gains) must skip that part, the
+    first backward has already added them."""
+    return _replay_depth > 0
+
+
 def _dx_node_names() -> set:
     return {f"{fn.__name__}Backward" for fn in LayerDW._dx_function_registry.values()}
 
@@ -401,6 +412,15 @@ def _leaves_below_dx(root) -> list:
 def partial_dx_recomputation(outputs, grad_outputs=None, retain_graph: bool = False) -> None:
     """Run the smallest backward that refills the ``grad_output`` stash of every
     ``LayerDW`` layer under ``outputs``."""
+    global _replay_depth
+    _replay_depth += 1
+    try:
+        _partial_dx_recomputation(outputs, grad_outputs, retain_graph)
+    finally:
+        _replay_depth -= 1
+
+
+def _partial_dx_recomputation(outputs, grad_outputs, retain_graph: bool) -> None:
     if grad_outputs is None:
         assert outputs.numel() == 1, "Implicit gradient outputs are only supported for scalar outputs"
         grad_outputs = torch.ones_like(outputs)

@@ -474,6 +474,40 @@ def test_single_node_layer_matches_the_composed_layer(dev, block):
         assert rel_err(g1[name], g0[name]) < 1e-2, name
 
 
+def test_partial_replay_through_a_single_node_layer(dev):
+    """B -> W recompute on the fused layer: the replay refills the output-gradient stashes of
+    the layer's linears with the values of the first backward and adds nothing to the norm
+    gains' gradients a second time."""
+    from elf_b200.models import llama as L
+    from elf_b200.zb_utils import LayerDW, partial_dx_recomputation, replace_layer_with_layer_dw
+
+    cfg = L.LlamaConfig(n_layers=1, d_model=512, n_heads=4, n_kv_heads=2, ffn=1536, vocab=1024, seq_len=256, rope_theta=500000.0)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        m = L.LlamaDecoderLayer(cfg).to(torch.bfloat16)
+    L.init_llama_(m, 0.02, 3)
+    replace_layer_with_layer_dw(m)
+    m.fused = True
+    layers = [mod for mod in m.modules() if isinstance(mod, LayerDW)]
+    x = torch.randn(2, cfg.seq_len, cfg.d_model, device=dev).bfloat16().requires_grad_()
+    g = torch.randn(2, cfg.seq_len, cfg.d_model, device=dev).bfloat16()
+    y = m(x)
+    for layer in layers:
+        layer.move_last_computed("input", 0)
+    y.backward(g, retain_graph=True)
+    first = [layer.last_grad_output.clone() for layer in layers]
+    gains = {n: p.grad.clone() for n, p in m.named_parameters() if "norm" in n}
+    assert gains and all(t is not None for t in first)
+    for layer in layers:
+        layer.last_grad_output = None
+    partial_dx_recomputation(y, g)
+    for layer, ref in zip(layers, first):
+        assert layer.last_grad_output is not None and rel_err(layer.last_grad_output, ref) < 1e-3
+    for n, p in m.named_parameters():
+        if "norm" in n:
+            assert torch.equal(p.grad, gains[n]), n
+
+
 def test_chunked_head_loss_matches_the_plain_head(dev):
     """LM head + cross entropy with the vocabulary in chunks (ragged last chunk, an ignored row)
     against fp32 logits: loss, hidden-state gradient, weight gradient added to what is there."""
