@@ -285,7 +285,6 @@ def _list_schedule(
     cost_w: float = 1,
     hop: float = 0,
     stage_costs: Optional[Sequence[float]] = None,
-    w_patience: float = 0.0,
 ) -> List[Operation]:
     """Greedy event-driven simulation of the whole pipeline.
 
@@ -403,14 +402,6 @@ def _list_schedule(
             continue
         if split_w:
             cand_w = [s for s in stages if w_next[s] < b_next[s]]
-            if cand_w and w_patience > 0.0:
-                # a backward (or forward) that is already on its way would find the rank busy with
-                # a weight-gradient pass it cannot interrupt: rather idle for a short while
-                soon = [x for x in list(b_times.values()) + ([] if capped else list(f_times.values())) if x is not None and x > t + EPS]
-                if soon and min(soon) - t < w_patience * min(dur_w[s] for s in cand_w):
-                    free_at[r] = min(soon)
-                    stalled_rounds = 0
-                    continue
             if cand_w:
                 s = min(cand_w, key=lambda s: (w_next[s], s))
                 out.W(s, w_next[s])
