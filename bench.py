@@ -161,8 +161,9 @@ def run_ours(args):
             # stage (the analytic stage costs above are only the starting point); the remaining
             # warm-up steps and everything timed run the re-laid schedule
             calibrated = pipe.measured_stage_costs()
-            pipe.set_scheduler(functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=calibrated))
-            sched_note = "zbv (list-scheduled for the F / B / W time of every stage measured in a warm-up step, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator)"
+            # robust: the durations drift by a percent or two per rank over the following steps; keep a layout that stays short when they do
+            pipe.set_scheduler(functools.partial(generate_zbv_schedule, cap="auto", cap_limit=6 * pp, stage_costs=calibrated, robust=0.02))
+            sched_note = "zbv (list-scheduled for the F / B / W time of every stage measured in a warm-up step, live-activation cap per rank chosen in [2p, 6p] by the timeline simulator over perturbed copies of those times)"
     # ---- device-timed region: inputs resident on the device -------------------------
     resident = [to_device(next(it)) for _ in range(args.steps)]
     fence()

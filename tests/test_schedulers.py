@@ -231,3 +231,25 @@ def test_headline_zbv_configuration_replays_without_deadlock(pp):
         ordered = COMM_SCHEDULERS[comm](list(full))
         check_schedule_validity(ordered)
         replay_comms(ordered, placement)
+
+
+def test_robust_zbv_layout_is_valid_and_deterministic():
+    """``robust > 0``: candidates laid out for perturbed costs, scored over perturbed scenarios; the
+    result is a complete ZB-V program, the same on every call (ranks derive it independently), and
+    not longer on the nominal costs than 3 % over the plain choice."""
+    from elf_b200.scheduling.schedulers import generate_zbv_schedule
+    from elf_b200.scheduling.simulator import simulate
+
+    p, n = 4, 8
+    placement = list(range(p)) + list(range(p - 1, -1, -1))
+    costs = [(1.0 + 0.05 * s, 1.3 + 0.02 * s, 0.8) for s in range(2 * p)]
+    costs[-1] = (1.6, 1.7, 1.5)
+    which = {OperationType.FORWARD: 0, OperationType.BACKWARD_INPUTS: 1, OperationType.BACKWARD_PARAMS: 2}
+    dur = lambda op: costs[op.block_id][which[op.op]] if op.op in which else 0.0
+    plain = generate_zbv_schedule(placement, n, cap="auto", stage_costs=costs)
+    a = generate_zbv_schedule(placement, n, cap="auto", stage_costs=costs, robust=0.02)
+    b = generate_zbv_schedule(placement, n, cap="auto", stage_costs=costs, robust=0.02)
+    assert [(o.op, o.block_id, o.mb_id, o.rank) for o in a] == [(o.op, o.block_id, o.mb_id, o.rank) for o in b]
+    for kind in which:
+        assert sorted((o.block_id, o.mb_id) for o in a if o.op == kind) == sorted((s, m) for s in range(2 * p) for m in range(n))
+    assert simulate(a, placement, dur).makespan <= 1.03 * simulate(plain, placement, dur).makespan
