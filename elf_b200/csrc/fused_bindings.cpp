@@ -195,23 +195,31 @@ void ce_chunk_grad(at::Tensor& logits, const at::Tensor& targets, const at::Tens
         "cross_entropy_chunk_grad");
 }
 
-at::Tensor embedding_fwd(const at::Tensor& table, const at::Tensor& ids) {
+int* status_ptr(const c10::optional<at::Tensor>& status, const at::Tensor& like) {
+  if (!status.has_value()) return nullptr;
+  TORCH_CHECK(status->is_cuda() && status->scalar_type() == at::kInt && status->numel() >= 4 && status->get_device() == like.get_device(),
+              "status must be an int32[4] tensor on the same device");
+  return status->data_ptr<int>();
+}
+
+at::Tensor embedding_fwd(const at::Tensor& table, const at::Tensor& ids, const c10::optional<at::Tensor>& status) {
   need_bf16(table, "table");
   TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.is_cuda(), "ids must be contiguous int64 CUDA");
   c10::cuda::CUDAGuard g(table.device());
   auto sizes = ids.sizes().vec();
   sizes.push_back(table.size(1));
   auto out = at::empty(sizes, table.options());
-  check(elfb::embedding_forward(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), (int)ids.numel(), (int)table.size(1), cur()),
+  check(elfb::embedding_forward(table.data_ptr(), ids.data_ptr<int64_t>(), out.data_ptr(), (int)ids.numel(), (int)table.size(1),
+                                (long long)table.size(0), status_ptr(status, table), cur()),
         "embedding_forward");
   return out;
 }
-void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dtable) {
+void embedding_bwd(const at::Tensor& dout, const at::Tensor& ids, at::Tensor& dtable, const c10::optional<at::Tensor>& status) {
   need_bf16(dout, "dout");
   TORCH_CHECK(dtable.is_contiguous() && (dtable.scalar_type() == at::kFloat || dtable.scalar_type() == at::kBFloat16), "dtable must be fp32 or bf16");
   c10::cuda::CUDAGuard g(dout.device());
   check(elfb::embedding_backward(dout.data_ptr(), ids.data_ptr<int64_t>(), dtable.data_ptr(), dtable.scalar_type() == at::kFloat,
-                                 (int)ids.numel(), (int)dtable.size(1), cur()),
+                                 (int)ids.numel(), (int)dtable.size(1), (long long)dtable.size(0), status_ptr(status, dout), cur()),
         "embedding_backward");
 }
 
@@ -276,8 +284,9 @@ void register_fused_ops(pybind11::module_& m) {
         py::arg("col0"), py::arg("first"));
   m.def("ce_chunk_grad", &ce_chunk_grad, py::arg("logits"), py::arg("targets"), py::arg("lse"), py::arg("gscale") = c10::nullopt, py::arg("scale") = 1.0,
         py::arg("col0") = 0, py::arg("vocab") = 0, py::arg("ignore_index") = -100);
-  m.def("embedding_fwd", &embedding_fwd);
-  m.def("embedding_bwd", &embedding_bwd);
+  m.def("embedding_fwd", &embedding_fwd, "table[ids]; an id outside the table gives a zero row and is recorded in status", py::arg("table"), py::arg("ids"),
+        py::arg("status") = c10::nullopt);
+  m.def("embedding_bwd", &embedding_bwd, py::arg("dout"), py::arg("ids"), py::arg("dtable"), py::arg("status") = c10::nullopt);
   m.def("embedding_bwd_sorted", &embedding_bwd_sorted);
   m.def("adamw", &adamw, py::arg("param"), py::arg("grad"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("lr"),
         py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0, py::arg("status") = c10::nullopt);

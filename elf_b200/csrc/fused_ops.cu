@@ -695,29 +695,54 @@ __global__ void __launch_bounds__(CE_THREADS) ce_chunk_grad_kernel(__nv_bfloat16
 }
 
 // ------------------------------------------------------------------------------ embedding
+// Error word shared with the GEMM / attention kernels (sm100_ptx.cuh): status[0] = code, [1] = where, [2..3] = detail.
+constexpr int kStatusOk = 0, kStatusBadIndex = 4;
+__device__ __forceinline__ void report_error(int* status, int code, int where, int a, int b) {
+  if (status != nullptr && atomicCAS(status, kStatusOk, code) == kStatusOk) {
+    status[1] = where;
+    status[2] = a;
+    status[3] = b;
+  }
+}
+
+// A token id outside [0, vocab) reads nothing: its output row is zero, its gradient is dropped, and
+// the first such id is recorded in the status word (code 4; where = 1 forward, 2 backward;
+// detail = row, id), which the optimizer step and the next pipeline step turn into an exception.
 __global__ void embedding_fwd_kernel(const Bf16x8* __restrict__ table, const int64_t* __restrict__ ids, Bf16x8* __restrict__ out,
-                                     long long total, int dim8) {
+                                     long long total, int dim8, long long vocab, int* __restrict__ status) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long row = idx / dim8;
   const int c = idx % dim8;
-  out[idx] = table[ids[row] * dim8 + c];
+  const int64_t id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (c == 0) report_error(status, kStatusBadIndex, 1, (int)row, (int)id);
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    out[idx] = pack8(zero);
+    return;
+  }
+  out[idx] = table[id * dim8 + c];
 }
 template <bool F32>
 __global__ void embedding_bwd_kernel(const __nv_bfloat162* __restrict__ dout, const int64_t* __restrict__ ids, void* __restrict__ dtable,
-                                     long long total, int dim2) {
+                                     long long total, int dim2, long long vocab, int* __restrict__ status) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long row = idx / dim2;
   const int c = idx % dim2;
+  const int64_t id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (c == 0) report_error(status, kStatusBadIndex, 2, (int)row, (int)id);
+    return;
+  }
   const __nv_bfloat162 g = dout[idx];
   if (F32) {
-    float* d = reinterpret_cast<float*>(dtable) + (ids[row] * dim2 + c) * 2;
+    float* d = reinterpret_cast<float*>(dtable) + (id * dim2 + c) * 2;
     const float2 f = __bfloat1622float2(g);
     atomicAdd(d, f.x);
     atomicAdd(d + 1, f.y);
   } else {
-    atomicAdd(reinterpret_cast<__nv_bfloat162*>(dtable) + ids[row] * dim2 + c, g);
+    atomicAdd(reinterpret_cast<__nv_bfloat162*>(dtable) + id * dim2 + c, g);
   }
 }
 
@@ -1035,22 +1060,23 @@ cudaError_t cross_entropy_chunk_grad(void* logits, const int64_t* targets, const
   return cudaGetLastError();
 }
 
-cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s) {
+cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, long long vocab, int* status,
+                              cudaStream_t s) {
   if (dim % 8) return cudaErrorInvalidValue;
   const long long total = (long long)rows * (dim / 8);
   if (total == 0) return cudaSuccess;
-  embedding_fwd_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)table, ids, (Bf16x8*)out, total, dim / 8);
+  embedding_fwd_kernel<<<blocks_for(total, 256), 256, 0, s>>>((const Bf16x8*)table, ids, (Bf16x8*)out, total, dim / 8, vocab, status);
   return cudaGetLastError();
 }
-cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim,
-                               cudaStream_t s) {
+cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim, long long vocab,
+                               int* status, cudaStream_t s) {
   if (dim % 2) return cudaErrorInvalidValue;
   const long long total = (long long)rows * (dim / 2);
   if (total == 0) return cudaSuccess;
   if (dtable_f32)
-    embedding_bwd_kernel<true><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
+    embedding_bwd_kernel<true><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2, vocab, status);
   else
-    embedding_bwd_kernel<false><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2);
+    embedding_bwd_kernel<false><<<blocks_for(total, 256), 256, 0, s>>>((const __nv_bfloat162*)dout, ids, dtable, total, dim / 2, vocab, status);
   return cudaGetLastError();
 }
 

@@ -56,15 +56,18 @@ cudaError_t cross_entropy_chunk_stats(const void* logits, const int64_t* targets
                                       int width, long long ld, long long col0, bool first, cudaStream_t s);
 cudaError_t cross_entropy_chunk_grad(void* logits, const int64_t* targets, const float* lse, const float* gscale, float scale, int rows, int width,
                                      long long ld, long long col0, long long vocab, int64_t ignore_index, cudaStream_t s);
-cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t s);
-// dtable[ids[row]] += dout[row]   (fp32 or bf16 table gradient; atomics)
+// out[row] = table[ids[row]].  An id outside [0, vocab) gives a zero row (no access) and, when `status`
+// (int[4], may be null) still reads 0, records {4, 1 forward / 2 backward, row, id} there.
+cudaError_t embedding_forward(const void* table, const int64_t* ids, void* out, int rows, int dim, long long vocab, int* status,
+                              cudaStream_t s);
+// dtable[ids[row]] += dout[row]   (fp32 or bf16 table gradient; atomics; ids outside [0, vocab) skipped and recorded)
 // grad[sorted_ids[k]] += dout[perm[k]] for every k, deterministically: equal ids are adjacent in
 // `sorted_ids` (ascending, stable), one CTA sums a run in order and adds it to the gradient row
 // (bf16 or fp32) in place.  Ids outside [0, vocab) are skipped.
 cudaError_t embedding_backward_sorted(const void* dout, const int64_t* sorted_ids, const int64_t* perm, void* grad, bool grad_f32, int rows,
                                       int dim, long long vocab, cudaStream_t s);
-cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim,
-                               cudaStream_t s);
+cudaError_t embedding_backward(const void* dout, const int64_t* ids, void* dtable, bool dtable_f32, int rows, int dim, long long vocab,
+                               int* status, cudaStream_t s);
 
 // Fused AdamW over flat buffers: bf16 params, fp32 master/m/v, grads bf16 or fp32.
 //   g' = g * grad_scale; m = b1 m + (1-b1) g'; v = b2 v + (1-b2) g'^2

@@ -24,7 +24,9 @@ enum : int {
   kErrBarrierTimeout = 1,   // an mbarrier wait ran past its time limit
   kErrPeerTimeout = 2,      // a wait on a flag written by another GPU ran past its limit
   kErrBadShape = 3,
+  kErrBadIndex = 4,         // an index read from memory (a token id) lies outside its table; the access was skipped
 };
+
 
 // Every spin in this code base is bounded by wall time measured with %globaltimer.
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s

@@ -213,7 +213,11 @@ class _Embedding(torch.autograd.Function):
         ctx.save_for_backward(ids)
         ctx.table = table if into_grad else None
         ctx.shape = table.shape
-        return _ext.get().embedding_fwd(table, ids.contiguous())
+        from . import gemm as _gemm
+
+        # an id outside the table reads nothing (zero row) and leaves a record that the optimizer
+        # step and the next pipeline step raise on
+        return _ext.get().embedding_fwd(table, ids.contiguous(), _gemm.status(table.device))
 
     @staticmethod
     def backward(ctx, dout):

@@ -80,7 +80,7 @@ def check_status(device=None) -> None:
 
 
 _SNAPSHOT: Dict[int, tuple] = {}  # device index -> (pinned int32[4], event of the last copy into it)
-_WHAT = {1: "an mbarrier wait timed out", 2: "a wait on a peer GPU timed out", 3: "bad shape"}
+_WHAT = {1: "an mbarrier wait timed out", 2: "a wait on a peer GPU timed out", 3: "bad shape", 4: "an index outside its table (detail: 1 forward / 2 backward, row, index)"}
 
 
 def snapshot_status_async(device=None) -> None:

@@ -474,6 +474,28 @@ def test_single_node_layer_matches_the_composed_layer(dev, block):
         assert rel_err(g1[name], g0[name]) < 1e-2, name
 
 
+def test_embedding_skips_and_records_an_id_outside_the_table(dev):
+    """An out-of-range token id must not become an out-of-range read: its row comes back zero, its
+    gradient is dropped, and the status word says which row and id."""
+    from elf_b200.ops import fused as Fu
+    from elf_b200.ops import gemm
+
+    torch.cuda.synchronize()
+    gemm.check_status()
+    table = torch.nn.Parameter(torch.randn(64, 32, device=dev).bfloat16())
+    ids = torch.tensor([[3, 64, 5, -2]], device=dev)
+    out = Fu.embedding(table, ids, into_grad=True)
+    assert torch.equal(out[0, 0], table[3]) and torch.equal(out[0, 2], table[5])
+    assert out[0, 1].abs().sum() == 0 and out[0, 3].abs().sum() == 0
+    out.float().sum().backward()
+    assert table.grad[3].float().sum() == 32 and table.grad.float().sum() == 64  # rows 3 and 5 only
+    rec = gemm.status(dev).tolist()
+    assert rec[0] == 4 and rec[1] == 1 and (rec[2], rec[3]) in ((1, 64), (3, -2))
+    with pytest.raises(RuntimeError, match="index outside its table"):
+        gemm.check_status()
+    gemm.check_status()  # the record is cleared by the check that raised
+
+
 def test_partial_replay_through_a_single_node_layer(dev):
     """B -> W recompute on the fused layer: the replay refills the output-gradient stashes of
     the layer's linears with the values of the first backward and adds nothing to the norm
