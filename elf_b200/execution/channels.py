@@ -215,9 +215,9 @@ class Channel:
 class _CopyLink:
     """One end of a channel on the copy transport.
 
-    Every rank of the pipeline holds one symmetric arena with a region per channel at the same
-    offset: ``depth`` slots of ``slot_bytes`` followed by a flag area.  The consumer's copy of the
-    region holds the ring; flag 0 of the consumer = sequence number
+    Every rank of the pipeline holds one symmetric arena.  The consumer's arena has the channel's
+    ring (``depth`` slots of ``slot_bytes``) followed by a flag area, the producer's arena a flag
+    area; flag 0 of the consumer = sequence number
     of the newest message that has landed, flag 1 of the producer = newest message the consumer
     has copied out (so slot reuse never overtakes the consumer).  Messages are numbered 1, 2, ...
     for the life of the channel and must be taken in the order they were posted, which is the
@@ -225,10 +225,12 @@ class _CopyLink:
 
     FLAG_BYTES = 256
 
-    def __init__(self, channel: "Channel", arena: torch.Tensor, peer_arena: torch.Tensor, peer_base_addr: int, offset: int, slot_bytes: int, depth: int, timeout_ms: float):
-        """``arena`` is this rank's symmetric buffer, ``peer_arena`` the peer's copy of it as mapped
-        here (``peer_base_addr`` its device address); the channel's region starts ``offset`` bytes
-        in on both: ``depth`` slots of ``slot_bytes``, then ``FLAG_BYTES`` of flags."""
+    def __init__(self, channel: "Channel", arena: torch.Tensor, peer_arena: torch.Tensor, peer_base_addr: int, at_producer: int, at_consumer: int,
+                 slot_bytes: int, depth: int, timeout_ms: float, producer: bool):
+        """``arena`` is this rank's symmetric buffer, ``peer_arena`` the peer's as mapped here
+        (``peer_base_addr`` its device address).  The channel's region in the consumer's arena
+        starts at ``at_consumer`` (``depth`` slots of ``slot_bytes``, then ``FLAG_BYTES`` of flags), its
+        region in the producer's arena at ``at_producer`` (``FLAG_BYTES`` of flags)."""
         from ..ops import _ext
         from ..ops import gemm as _gemm
 
@@ -239,11 +241,18 @@ class _CopyLink:
         self.channel = channel
         self.device = channel.device
         self.depth, self.slot_bytes, self.timeout_ms = depth, slot_bytes, timeout_ms
+        self.producer = producer
         ring = depth * slot_bytes
-        self.buf = arena[offset : offset + ring]
-        self.flags = arena[offset + ring : offset + ring + self.FLAG_BYTES].view(torch.int32)
-        self.peer_buf = peer_arena[offset : offset + ring]
-        self.peer_flag_addr = peer_base_addr + offset + ring
+        if producer:
+            self.buf = None
+            self.flags = arena[at_producer : at_producer + self.FLAG_BYTES].view(torch.int32)
+            self.peer_buf = peer_arena[at_consumer : at_consumer + ring]
+            self.peer_flag_addr = peer_base_addr + at_consumer + ring
+        else:
+            self.buf = arena[at_consumer : at_consumer + ring]
+            self.flags = arena[at_consumer + ring : at_consumer + ring + self.FLAG_BYTES].view(torch.int32)
+            self.peer_buf = None
+            self.peer_flag_addr = peer_base_addr + at_producer
         self.status = _gemm.status(self.device)
         self.stream = torch.cuda.Stream(self.device)  # producer side: copies run here, behind the compute stream's event
         self.sent = 0  # producer: messages sent
@@ -298,6 +307,27 @@ class _CopyLink:
         return out
 
 
+def _arena_layout(sizes: List[int], roles: Dict[int, Tuple[int, int]], world: int, depth: int):
+    """Where every channel lives in the ranks' symmetric arenas.  ``sizes[idx]`` is the largest
+    message of channel ``idx`` (0: unused so far, the channel stays on NCCL), ``roles[idx]`` its
+    ``(producer, consumer)`` ranks.  The consumer's arena holds the channel's ring and the flag
+    the producer raises; the producer's arena holds only the flag the consumer raises.  Returns
+    ``({idx: (offset in the producer's arena, offset in the consumer's arena, slot bytes)}, arena
+    bytes)``; every rank computes the same table (it needs its peers' offsets), and all arenas
+    have one size, that of the fullest."""
+    cursor = [0] * world
+    offsets = {}
+    for idx, nbytes in enumerate(sizes):
+        if nbytes == 0:
+            continue
+        producer, consumer = roles[idx]
+        slot = (nbytes + 255) // 256 * 256
+        offsets[idx] = (cursor[producer], cursor[consumer], slot)
+        cursor[consumer] += depth * slot + _CopyLink.FLAG_BYTES
+        cursor[producer] += _CopyLink.FLAG_BYTES
+    return offsets, max(cursor)
+
+
 class ChannelTable:
     """All channels touching this rank, keyed by ``(src_block, dst_block, direction, k)``
     where ``src_block`` is the block the *payload* comes from and ``k`` numbers the tensors
@@ -322,6 +352,11 @@ class ChannelTable:
         self.pp_group, self.n_channel_ids, self.device = pp_group, n, device
         self._arena = None
         self._order: List[Tuple[int, int, str, int]] = []  # this rank's channels in creation order (the same relative order on both ends)
+        # channel index -> (producer, consumer) as pipeline-local ranks, for every channel of the pipeline
+        self._roles: Dict[int, Tuple[int, int]] = {}
+        for i, (a, b, k) in enumerate(edges):
+            self._roles[2 * i] = (placement[a], placement[b])  # forward: a's output travels to b
+            self._roles[2 * i + 1] = (placement[b], placement[a])  # backward: b's input gradient travels to a
         self.transport = "nccl" if backend == "nccl" else backend
         for replica in range(dp if dedicated_groups else 1):
             if not dedicated_groups:
@@ -343,6 +378,7 @@ class ChannelTable:
                     peer_local = rb if local_rank == ra else ra
                     ch = Channel(src, dst, direction, offset + peer_local, group, device, 2 * i + j, n)
                     ch.peer_local = peer_local  # the peer's rank inside the pipeline group
+                    ch.is_producer = local_rank == placement[src]
                     self.channels[(src, dst, direction, k)] = ch
                     self._order.append((src, dst, direction, k))
 
@@ -355,8 +391,9 @@ class ChannelTable:
         pipeline group (every rank of the job calls it at the same point between two steps):
 
         1. the ranks gather the largest message every channel has carried;
-        2. every rank allocates ONE symmetric arena laid out identically - a region per channel
-           (``depth`` slots + flags) - and the group maps the arenas in a single rendezvous.  (One
+        2. every rank allocates ONE symmetric arena - the consuming end of a channel holds its ring
+           (``depth`` slots) and a flag, the producing end a flag - and the group maps the arenas in
+           a single rendezvous.  (One
            rendezvous per pipeline, entered by all of its ranks: the exchange behind it numbers its
            rounds per process, so ranks that had rendezvoused pairwise a different number of times
            would never meet.)
@@ -379,13 +416,7 @@ class ChannelTable:
         for part in gathered:
             for idx, nbytes in part.items():
                 sizes[idx] = max(sizes[idx], nbytes)
-        offsets, total = {}, 0
-        for idx, nbytes in enumerate(sizes):
-            if nbytes == 0:
-                continue  # never used so far: stays on NCCL
-            slot = (nbytes + 255) // 256 * 256
-            offsets[idx] = (total, slot)
-            total += depth * slot + _CopyLink.FLAG_BYTES
+        offsets, total = _arena_layout(sizes, self._roles, world, depth)
         if total == 0:
             return 0
         arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
@@ -400,11 +431,11 @@ class ChannelTable:
             ch = self.channels[key]
             if ch.link is not None or ch.index not in offsets:
                 continue
-            off, slot = offsets[ch.index]
+            at_producer, at_consumer, slot = offsets[ch.index]
             if ch.peer_local not in peers:
                 peers[ch.peer_local] = (handle.get_buffer(ch.peer_local, (total,), torch.uint8), int(handle.buffer_ptrs[ch.peer_local]))
             peer_arena, peer_addr = peers[ch.peer_local]
-            ch.attach_link(_CopyLink(ch, arena, peer_arena, peer_addr, off, slot, depth, timeout_ms))
+            ch.attach_link(_CopyLink(ch, arena, peer_arena, peer_addr, at_producer, at_consumer, slot, depth, timeout_ms, ch.is_producer))
             switched += 1
         self.transport = "copy"
         return switched
