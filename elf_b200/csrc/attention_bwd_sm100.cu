@@ -500,6 +500,7 @@ const char* attention_backward(const AttnBwdArgs& a, cudaStream_t stream) {
   attn_bwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, tdo, tdq, a.lse2, a.delta, static_cast<__nv_bfloat16*>(a.dqkv), a.dq_acc, a.batch, a.seq, a.n_heads,
                                                              a.n_kv_heads, scale, a.status);
   attn_bwd_finish<<<num_sms * 8, 256, 0, stream>>>(a.dq_acc, static_cast<__nv_bfloat16*>(a.dqkv), (long long)tokens, (int)q_cols, (int)pitch);
+  flush_bounds_record(a.status, stream);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

@@ -483,6 +483,7 @@ const char* attention_forward(const AttnArgs& a, cudaStream_t stream) {
   const int grid = int(items < num_sms ? items : num_sms);
   attention_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tq, static_cast<__nv_bfloat16*>(a.out), a.lse, a.batch, a.seq, a.n_heads, a.n_kv_heads,
                                                                   scale * 1.4426950408889634f, a.status);
+  flush_bounds_record(a.status, stream);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

@@ -89,6 +89,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("accumulate") = false, py::arg("alpha") = 1.0, py::arg("status") = c10::nullopt, py::arg("variant") = 0,
         py::arg("split_tail") = true, py::arg("push_out") = std::vector<int64_t>(), py::arg("push_flags") = std::vector<int64_t>(),
         py::arg("push_flag_value") = 0, py::arg("push_counter") = c10::nullopt);
+  m.def("bounds_check_build", &elfb::bounds_check_build, "whether this library validates TMA coordinates on the device (-DELF_BOUNDS_CHECK)");
+  m.def("bounds_check_selftest", [](at::Tensor& status) {
+    TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 4, "status must be an int32[4] CUDA tensor");
+    c10::cuda::CUDAGuard guard(status.device());
+    const cudaError_t e = elfb::bounds_check_selftest(status.data_ptr<int>(), at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(e == cudaSuccess, "bounds_check_selftest: ", cudaGetErrorString(e));
+  }, "check build only: two copies with forbidden coordinates go through the checked wrappers (recorded, not issued)");
 #ifdef ELFB_WITH_DP_REDUCE
   register_dp_reduce(m);
 #endif

@@ -53,31 +53,41 @@ def sources():
     return out
 
 
-def build(verbose: bool = False):
-    """Compile (incrementally, through ninja) and import the extension module."""
+CHECK_NAME = "elf_b200_C_check"
+CHECK_BUILD_DIR = HERE / "_build_check"
+
+
+def build(verbose: bool = False, bounds_check: bool = False):
+    """Compile (incrementally, through ninja) and import the extension module.  With
+    ``bounds_check`` the debug variant is built instead (``-DELF_BOUNDS_CHECK``: tiled TMA copies
+    validate their coordinates on the device, record a violation in the status word and skip the
+    copy); it lives beside the regular build under another name and ``ELF_B200_BOUNDS_CHECK=1``
+    makes ``elf_b200.ops._ext`` load it."""
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 1)))
     from torch.utils import cpp_extension
 
-    BUILD_DIR.mkdir(exist_ok=True)
-    defines = []
+    build_dir = CHECK_BUILD_DIR if bounds_check else BUILD_DIR
+    build_dir.mkdir(exist_ok=True)
+    defines = ["-DELF_BOUNDS_CHECK"] if bounds_check else []
     if (HERE / "attention_sm100.cu").exists():
         defines.append("-DELFB_WITH_ATTENTION")
     if (HERE / "dp_reduce.cu").exists():
         defines.append("-DELFB_WITH_DP_REDUCE")
-    build_noalloc_library(verbose)
+    if not bounds_check:
+        build_noalloc_library(verbose)
     return cpp_extension.load(
-        name=NAME,
+        name=CHECK_NAME if bounds_check else NAME,
         sources=sources(),
         extra_cflags=["-O3", "-std=c++17"] + defines,
         extra_cuda_cflags=NVCC_FLAGS + defines,
         extra_ldflags=["-lcudart"],
-        build_directory=str(BUILD_DIR),
+        build_directory=str(build_dir),
         with_cuda=True,
         verbose=verbose,
     )
 
 
 if __name__ == "__main__":
-    mod = build(verbose="-v" in sys.argv)
+    mod = build(verbose="-v" in sys.argv, bounds_check="--bounds-check" in sys.argv)
     print("built", mod.__file__)

@@ -369,6 +369,7 @@ static cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, cons
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb2, tb4, d, bias, M, N, K, ldd, fmt, alpha, max_split, status, push);
+  flush_bounds_record(status, stream);
   return cudaGetLastError();
 }
 
@@ -417,5 +418,27 @@ const char* gemm_tcgen05(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   else e = dispatch_epilogue<true, false>(g, ta, tb, tb2, tb4, num_sms, stream);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
+
+#ifdef ELF_BOUNDS_CHECK
+namespace {
+// Issues a store and a reduce whose coordinates break the rules (odd x; negative y).  The checked
+// wrappers record the first one and skip both, so nothing reaches the hardware: the tensor map
+// pointer is never used.
+__global__ void bounds_selftest_kernel() {
+  tma_store_2d(nullptr, 0u, 3, 0);
+  tma_reduce_add_2d(nullptr, 0u, 8, -4);
+}
+}  // namespace
+
+bool bounds_check_build() { return true; }
+cudaError_t bounds_check_selftest(int* status, cudaStream_t stream) {
+  bounds_selftest_kernel<<<1, 1, 0, stream>>>();
+  flush_bounds_record(status, stream);
+  return cudaGetLastError();
+}
+#else
+bool bounds_check_build() { return false; }
+cudaError_t bounds_check_selftest(int*, cudaStream_t) { return cudaErrorNotSupported; }
+#endif
 
 }  // namespace elfb

@@ -30,4 +30,11 @@ const char* gemm_tcgen05(const GemmArgs& args, int num_sms, cudaStream_t stream)
 // Same contract, CTA-pair kernel (gemm_sm100_2cta.cu).
 const char* gemm_tcgen05_pair(const GemmArgs& args, int num_sms, cudaStream_t stream);
 
+// Whether this library was compiled with -DELF_BOUNDS_CHECK (tiled TMA copies validate their
+// coordinates, record a violation in the status word and skip the copy instead of trapping).
+bool bounds_check_build();
+// Check build only: runs two copies with forbidden coordinates through the checked wrappers; the
+// status word must read {5, 4, 3, 0} afterwards and nothing may have been issued.
+cudaError_t bounds_check_selftest(int* status, cudaStream_t stream);
+
 }  // namespace elfb

@@ -482,6 +482,7 @@ static cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
       return cudaErrorInvalidValue;
   }
   kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, g.d, g.bias, g.M, g.N, g.K, g.ldd, (uint32_t)g.fmt, g.alpha, max_split, group_m, g.status, g.push, peers);
+  flush_bounds_record(g.status, stream);
   return cudaGetLastError();
 }
 

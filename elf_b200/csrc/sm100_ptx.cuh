@@ -25,7 +25,52 @@ enum : int {
   kErrPeerTimeout = 2,      // a wait on a flag written by another GPU ran past its limit
   kErrBadShape = 3,
   kErrBadIndex = 4,         // an index read from memory (a token id) lies outside its table; the access was skipped
+  kErrBounds = 5,           // -DELF_BOUNDS_CHECK build only: a tiled TMA copy was given coordinates it must not run with
 };
+
+// ----------------------------------------------------------------------------------------
+// -DELF_BOUNDS_CHECK (debug build, `python -m elf_b200.csrc.build --bounds-check`): every tiled
+// TMA copy validates its coordinates before it is issued.  The hardware checks nothing about
+// them: an innermost coordinate whose byte offset is not a multiple of 16 ends the context with
+// "illegal instruction", and so does a store or reduce that starts at a negative coordinate.
+// A violation is recorded (first one wins: code, where, x, y) in a per-module device array and
+// the copy is made harmless instead of trapping: a load runs at coordinate (0, 0), so that its
+// mbarrier still completes, a store or reduce is skipped.  The launchers fold the record into
+// the caller's status word after each launch (`flush_bounds_record`).
+// ----------------------------------------------------------------------------------------
+#ifdef ELF_BOUNDS_CHECK
+static __device__ int g_bounds_record[4];
+
+__device__ __forceinline__ bool tma_coords_ok(int32_t x, int32_t y, int x_multiple, bool store, int where) {
+  constexpr int32_t kSane = 1 << 30;
+  const bool ok = x % x_multiple == 0 && (!store || (x >= 0 && y >= 0)) && x > -kSane && x < kSane && y > -kSane && y < kSane;
+  if (!ok && atomicCAS(&g_bounds_record[0], kOk, kErrBounds) == kOk) {
+    g_bounds_record[1] = where;
+    g_bounds_record[2] = x;
+    g_bounds_record[3] = y;
+  }
+  return ok;
+}
+
+static __global__ void flush_bounds_record_kernel(int* status) {
+  if (g_bounds_record[0] == kOk) return;
+  if (status != nullptr && atomicCAS(status, kOk, g_bounds_record[0]) == kOk) {
+    status[1] = g_bounds_record[1];
+    status[2] = g_bounds_record[2];
+    status[3] = g_bounds_record[3];
+  }
+  g_bounds_record[0] = kOk;
+}
+inline void flush_bounds_record(int* status, cudaStream_t stream) { flush_bounds_record_kernel<<<1, 1, 0, stream>>>(status); }
+#define ELFB_CHECK_LOAD(x, y, where) \
+  if (!tma_coords_ok(x, y, 8, false, where)) { x = 0; y = 0; }
+#define ELFB_CHECK_STORE(x, y, where) \
+  if (!tma_coords_ok(x, y, 4, true, where)) return;
+#else
+inline void flush_bounds_record(int*, cudaStream_t) {}
+#define ELFB_CHECK_LOAD(x, y, where)
+#define ELFB_CHECK_STORE(x, y, where)
+#endif
 
 
 // Every spin in this code base is bounded by wall time measured with %globaltimer.
@@ -116,18 +161,21 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, uint32_t bar, int32_t x, int32_t y) {
+  ELFB_CHECK_LOAD(x, y, 1)
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, uint32_t bar, int32_t x, int32_t y, int32_t z) {
+  ELFB_CHECK_LOAD(x, y, 2)
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar, int32_t x, int32_t y, int32_t z, int32_t w) {
+  ELFB_CHECK_LOAD(x, y, 3)
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
@@ -146,12 +194,14 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem, int32_t x, int32_t y) {
+  ELFB_CHECK_STORE(x, y, 4)
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
 }
 // global[tile] += shared[tile], element type taken from the tensor map (the add happens in L2)
 __device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, uint32_t src_smem, int32_t x, int32_t y) {
+  ELFB_CHECK_STORE(x, y, 5)
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
@@ -290,6 +340,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 // TMA load into this CTA's shared memory whose completion is signalled on an mbarrier that
 // may live in the peer CTA of the pair (no multicast: every CTA fetches its own tile).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  ELFB_CHECK_LOAD(x, y, 6)
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)

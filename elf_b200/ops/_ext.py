@@ -1,15 +1,20 @@
-"""Locate and load the compiled extension (``elf_b200/csrc/_build/elf_b200_C.so``)."""
+"""Locate and load the compiled extension (``elf_b200/csrc/_build/elf_b200_C.so``, or its
+bounds-checking variant ``elf_b200/csrc/_build_check/elf_b200_C_check.so``)."""
 
 from __future__ import annotations
 
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
 import torch
 
-_BUILD_DIR = Path(__file__).resolve().parent.parent / "csrc" / "_build"
-_NAME = "elf_b200_C"
+# ELF_B200_BOUNDS_CHECK=1 selects the debug variant (built with `python -m elf_b200.csrc.build --bounds-check`), whose
+# tiled TMA copies validate their coordinates on the device and record a violation in the status word
+_CHECKED = os.environ.get("ELF_B200_BOUNDS_CHECK", "0") not in ("", "0")
+_BUILD_DIR = Path(__file__).resolve().parent.parent / "csrc" / ("_build_check" if _CHECKED else "_build")
+_NAME = "elf_b200_C_check" if _CHECKED else "elf_b200_C"
 _module = None
 _load_error: Exception | None = None
 
@@ -20,7 +25,7 @@ def _try_load():
         return
     so = _BUILD_DIR / f"{_NAME}.so"
     if not so.exists():
-        _load_error = FileNotFoundError(f"{so} not found; run `python -m elf_b200.csrc.build`")
+        _load_error = FileNotFoundError(f"{so} not found; run `python -m elf_b200.csrc.build{' --bounds-check' if _CHECKED else ''}`")
         return
     try:
         spec = importlib.util.spec_from_file_location(_NAME, so)
