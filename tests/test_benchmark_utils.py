@@ -60,3 +60,21 @@ def _correctness_worker(rank, world):
 @pytest.mark.dist
 def test_check_correctness_two_ranks():
     run_ranks(_correctness_worker, 2)
+
+
+def test_offline_memory_plan_fits_the_budget():
+    """``benchmarks/plan_memory.py``: analytic stage statistics -> ILP.  A budget below the
+    unconstrained peak must be met by recomputation at the price of a longer planned step."""
+    from benchmarks.plan_memory import main as plan
+
+    free = plan(["--name", "llama-1.3b", "--pp", "2", "--nmb", "8", "--scheduler", "zbv", "--memory-budget-gb", "1000", "--time-limit", "30"])
+    assert free["slots"]["full_fwd"] + free["slots"]["activations_bwd"] + free["slots"]["full_bwd"] == 0
+    budget = 0.9 * max(free["peak_gb_per_rank"])
+    assert budget > max(free["resident_gb_per_rank"])
+    tight = plan(["--name", "llama-1.3b", "--pp", "2", "--nmb", "8", "--scheduler", "zbv", "--memory-budget-gb", f"{budget:.3f}", "--time-limit", "30"])
+    assert "infeasible" not in tight
+    assert max(tight["peak_gb_per_rank"]) <= budget + 0.06  # rounded to 0.1 GB in the report
+    assert sum(tight["slots"][k] for k in ("full_fwd", "activations_bwd", "full_bwd")) > 0
+    assert tight["planned_step_ms"] >= free["planned_step_ms"]
+    impossible = plan(["--name", "llama-1.3b", "--pp", "2", "--nmb", "8", "--scheduler", "zbv", "--memory-budget-gb", f"{0.5 * max(free['resident_gb_per_rank']):.3f}", "--time-limit", "10"])
+    assert "infeasible" in impossible
