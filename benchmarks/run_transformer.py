@@ -103,12 +103,22 @@ def main():
     assert args.batch_size is not None or args.nmb is not None, "Batch size or number of micro-batches must be provided"
     batch = args.mb_size * args.nmb if args.batch_size is None else args.batch_size
     assert batch % args.mb_size == 0
+    stored = None
     if args.scheduler == "file":
         with open(args.schedule_file) as f:
-            scheduler = SCHEDULERS["fixed"](json.load(f))
+            stored = json.load(f)
+        if "full_fwd" in stored:  # a stored ILP solution (benchmarks/plan_memory.py --out): its order plus its remat / offload tables
+            from benchmarks.ilp_schedulers import RematScheduler
+
+            scheduler = RematScheduler(stored)
+        else:
+            scheduler = SCHEDULERS["fixed"](stored)
     else:
         scheduler = args.scheduler
-    placement = Placement.default(args.scheduler, pp) * args.interleaving
+    if stored is not None and "placement" in stored:
+        placement = Placement(stored["placement"])
+    else:
+        placement = Placement.default(args.scheduler, pp) * args.interleaving
     if args.checkpointing:
         scheduler = get_checkpointed_scheduler(scheduler, args.checkpointing)
     elif args.offloading:

@@ -78,3 +78,28 @@ def test_offline_memory_plan_fits_the_budget():
     assert tight["planned_step_ms"] >= free["planned_step_ms"]
     impossible = plan(["--name", "llama-1.3b", "--pp", "2", "--nmb", "8", "--scheduler", "zbv", "--memory-budget-gb", f"{0.5 * max(free['resident_gb_per_rank']):.3f}", "--time-limit", "10"])
     assert "infeasible" in impossible
+
+
+def test_planned_solution_replays_through_the_benchmark_cli(tmp_path):
+    """Plan offline (a budget that forces recomputation), store the solution, and train with it:
+    ``run_transformer.py --scheduler file`` takes order, placement and remat tables from the file."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from benchmarks.plan_memory import main as plan
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = str(tmp_path / "plan.json")
+    report = plan(["--name", "llama-tiny", "--pp", "2", "--nmb", "4", "--scheduler", "zbv", "--memory-budget-gb", "0.026", "--time-limit", "20", "--out", path])
+    assert "infeasible" not in report and report["slots"]["full_fwd"] + report["slots"]["activations_bwd"] + report["slots"]["full_bwd"] > 0
+    with open(path) as fh:
+        stored = json.load(fh)
+    assert stored["placement"] == [0, 1, 1, 0] and len(stored["order"]) == 3 * 4 * 4
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29773",
+           os.path.join(root, "benchmarks", "run_transformer.py"), "--architecture", "llama", "--name", "llama-tiny", "--partitioner", "handcrafted",
+           "--scheduler", "file", "--schedule-file", path, "--nmb", "4", "--mb-size", "1", "--niters", "2", "--warmup", "1", "--backend", "gloo"]
+    out = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-3000:]
+    assert "tokens_per_s" in out.stdout
