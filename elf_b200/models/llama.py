@@ -431,6 +431,7 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
     return ranges, [stage_cost(bounds, s) for s in range(n_stages)]
 
 
+THIRDS_GAIN = 0.02  # simulated gain below which a cut with three points per layer is not worth its two-tensor boundaries
 FIRST_RANK_MARGIN = 0.15  # layer units per micro-batch kept free on rank 0 of a V placement when the cut allows for the pipeline's fill
 BOTTLENECK_SLACK = 0.005  # partitions whose busiest rank is this close to the smallest possible one compete on the second criterion
 LOAD_WEIGHT = 8.0  # weight of squared rank loads against squared stage costs when choosing among partitions within the bottleneck
@@ -636,7 +637,9 @@ def choose_llama_cut(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], 
     after SwiGLU; that boundary carries two tensors) or ``True`` (cuts between attention and MLP
     halves only).  On a V placement with a cost model that knows the number of micro-batches, both
     cuts are laid out as ZB-V schedules and run through the timeline simulator, and thirds are taken
-    when their step is at least 0.5 % shorter.  (The busiest rank's load alone misjudges it: on 8
+    when their step is at least ``THIRDS_GAIN`` (2 %) shorter: measured on 4 GPUs, a thirds cut whose
+    simulated step was 1 % shorter ran no faster than the halves (780-789 ms against 774-791 ms),
+    and its two-tensor boundaries cost memory for the second ring.  (The busiest rank's load alone misjudges it: on 8
     ranks with the Llama-3-8B shape the halves have the lighter busiest rank, 4.37 against 4.46
     layer units, but leave rank 0, which nothing can wait for, 2 % more work and the simulated and
     the measured step 4 % longer.)  Otherwise thirds are taken when they lower the busiest rank's
@@ -654,7 +657,7 @@ def choose_llama_cut(cfg: LlamaConfig, n_stages: int, placement: Sequence[int], 
     n_ranks = len(set(placement))
     is_v = n_stages == 2 * n_ranks and list(placement) == list(range(n_ranks)) + list(range(n_ranks - 1, -1, -1))
     if is_v and n_ranks > 1 and cost_model is not None and getattr(cost_model, "micro_batches", None):
-        return "thirds" if _simulated_step(cfg, n_stages, placement, "thirds", cost_model) < 0.995 * _simulated_step(cfg, n_stages, placement, True, cost_model) else True
+        return "thirds" if _simulated_step(cfg, n_stages, placement, "thirds", cost_model) < (1.0 - THIRDS_GAIN) * _simulated_step(cfg, n_stages, placement, True, cost_model) else True
     return "thirds" if busiest("thirds") < (1.0 - gain) * busiest(True) else True
 
 
