@@ -10,7 +10,7 @@ durations and the order each rank really ran them in, are replayed by the timeli
 (``elf_b200.scheduling.simulator``) with a given hop latency, which shows how much of the
 measured step the data-flow model explains.
 
-    python benchmarks/pipeline_timeline.py gpurun_out/timeline_n8.json [--hop-ms 0.15]
+    python benchmarks/pipeline_timeline.py timeline.json [--hop-ms 0.15]
 """
 
 from __future__ import annotations

@@ -80,6 +80,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const c10::op
 
 void register_fused_ops(pybind11::module_& m);
 void register_host_runtime(pybind11::module_& m);
+void register_symm_runtime(pybind11::module_& m);
 void register_dp_reduce(pybind11::module_& m);
 void register_attention(pybind11::module_& m);
 
@@ -104,4 +105,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
   register_fused_ops(m);
   register_host_runtime(m);
+  register_symm_runtime(m);
 }

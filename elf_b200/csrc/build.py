@@ -13,7 +13,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 BUILD_DIR = HERE / "_build"
 NAME = "elf_b200_C"
-SOURCES = ["bindings.cpp", "fused_bindings.cpp", "host_runtime.cpp", "gemm_sm100.cu", "gemm_sm100_2cta.cu", "fused_ops.cu"]
+SOURCES = ["bindings.cpp", "fused_bindings.cpp", "host_runtime.cpp", "symm_runtime.cpp", "gemm_sm100.cu", "gemm_sm100_2cta.cu", "fused_ops.cu"]
 OPTIONAL_SOURCES = ["attention_sm100.cu", "attention_bwd_sm100.cu", "attention_bindings.cpp", "dp_reduce.cu", "p2p_signal.cu", "dp_reduce_bindings.cpp"]
 NVCC_FLAGS = [
     "-gencode",

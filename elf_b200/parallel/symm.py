@@ -1,22 +1,37 @@
 """Symmetric memory: buffers that every rank of a group allocates at the same size and that
 every other rank of the group can address directly over NVLink.
 
-Allocation, handle exchange and peer mapping are delegated to
-``torch.distributed._symmetric_memory`` (CUDA virtual-memory handles exchanged through the
-group's store).  What this module adds is the view the kernels need: raw peer addresses,
-and a single-process stand-in (``LocalSymmetricGroup``) in which several *virtual ranks*
-live on one GPU so that the push/finalize protocol can be exercised end to end on one
-device (kernels that never wait on a later launch are safe to run back to back).
+Two providers, chosen with ``ELF_B200_SYMM``:
+
+``torch`` (default)  allocation, handle exchange and peer mapping by
+                     ``torch.distributed._symmetric_memory`` (CUDA virtual-memory handles exchanged
+                     through the group's store);
+``vmm``              this package's own runtime (``csrc/symm_runtime.cpp``): every rank creates one
+                     physical allocation with the CUDA virtual-memory API, exports it as a file
+                     descriptor, the descriptors travel between the processes of the node over
+                     UNIX-domain sockets (``SCM_RIGHTS``), and every rank maps its peers'
+                     allocations.  No multicast object is bound: the consumers here (gradient push,
+                     stage-to-stage rings) are point-to-point stores.
+
+What this module adds on top is the view the kernels need: raw peer addresses, and a
+single-process stand-in (``LocalSymmetricGroup``) in which several *virtual ranks* live on one
+GPU so that the push/finalize protocol can be exercised end to end on one device (kernels that
+never wait on a later launch are safe to run back to back).
 """
 
 from __future__ import annotations
 
+import os
+import socket
+import tempfile
+import threading
+import uuid
 from typing import List, Sequence
 
 import torch
 import torch.distributed as dist
 
-__all__ = ["SymmetricBuffer", "LocalSymmetricGroup"]
+__all__ = ["SymmetricBuffer", "LocalSymmetricGroup", "exchange_fds"]
 
 
 class SymmetricBuffer:
@@ -30,9 +45,11 @@ class SymmetricBuffer:
 
     @staticmethod
     def allocate(numel: int, dtype: torch.dtype, group, device=None) -> "SymmetricBuffer":
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if os.environ.get("ELF_B200_SYMM", "torch") == "vmm":
+            return _allocate_vmm(numel, dtype, group, device)
         import torch.distributed._symmetric_memory as symm_mem
 
-        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         t = symm_mem.empty(numel, dtype=dtype, device=device)
         handle = symm_mem.rendezvous(t, group=group.group_name if hasattr(group, "group_name") else group)
         t.zero_()
@@ -44,6 +61,77 @@ class SymmetricBuffer:
 
     def peer_address(self, peer: int, byte_offset: int = 0) -> int:
         return self.addresses[peer] + byte_offset
+
+
+def exchange_fds(my_fd: int, group) -> List[int]:
+    """Give every other rank of ``group`` (processes of one node) a duplicate of ``my_fd`` and return
+    theirs, indexed by group rank (``-1`` at this rank's own index).  Each rank listens on a
+    UNIX-domain socket whose path the ranks publish with ``all_gather_object``; descriptors cross
+    as ancillary data (``SCM_RIGHTS``), which is how a CUDA allocation exported as a POSIX file
+    descriptor reaches the process that imports it."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    path = os.path.join(tempfile.gettempdir(), f"elf_b200_symm_{uuid.uuid4().hex}_{rank}.sock")
+    server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    server.bind(path)
+    server.listen(world)
+    received: List[int] = [-1] * world
+    errors: List[BaseException] = []
+
+    def accept_all():
+        try:
+            for _ in range(world - 1):
+                conn, _addr = server.accept()
+                with conn:
+                    msg, fds, _flags, _a = socket.recv_fds(conn, 16, 1)
+                    received[int(msg.decode())] = fds[0]
+        except BaseException as exc:  # surfaced on the caller's thread below
+            errors.append(exc)
+
+    listener = threading.Thread(target=accept_all, daemon=True)
+    listener.start()
+    try:
+        paths: List[str] = [""] * world
+        dist.all_gather_object(paths, path, group=group)
+        for peer in range(world):
+            if peer == rank:
+                continue
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as conn:
+                conn.connect(paths[peer])
+                socket.send_fds(conn, [str(rank).encode()], [my_fd])
+        listener.join(timeout=120)
+        if listener.is_alive() or errors:
+            raise RuntimeError(f"exchange of memory handles did not complete: {errors[0] if errors else 'a peer never connected'}")
+    finally:
+        server.close()
+        try:
+            os.unlink(path)
+        except OSError:
+            pass
+    return received
+
+
+def _allocate_vmm(numel: int, dtype: torch.dtype, group, device) -> "SymmetricBuffer":
+    """``SymmetricBuffer.allocate`` on this package's own runtime (``VmmArena``)."""
+    from ..ops import _ext
+
+    ext = _ext.get()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+    arena = ext.VmmArena(nbytes, device.index if device.index is not None else torch.cuda.current_device())
+    fd = arena.export_fd()
+    try:
+        theirs = exchange_fds(fd, group)
+    finally:
+        os.close(fd)
+    addresses = [0] * world
+    for peer in range(world):
+        addresses[peer] = arena.address if peer == rank else arena.peer_address(arena.import_peer(theirs[peer]))
+    local = arena.tensor()[:nbytes].view(dtype)
+    buf = SymmetricBuffer(local, addresses, rank)
+    buf._handle = arena  # owns the allocation and the peer mappings
+    torch.cuda.synchronize(device)
+    dist.barrier(group=group)  # nobody touches a peer's buffer before every rank has mapped it
+    return buf
 
 
 class LocalSymmetricGroup:
