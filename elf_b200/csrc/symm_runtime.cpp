@@ -161,8 +161,15 @@ class VmmArena {
     m = Mapping{};
   }
   at::Tensor view(const Mapping& m) const {
-    auto options = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, static_cast<c10::DeviceIndex>(device_));
-    return at::from_blob(reinterpret_cast<void*>(m.ptr), {static_cast<int64_t>(m.bytes)}, [](void*) {}, options);
+    // The view belongs to THIS rank's device whichever GPU holds the memory: a peer's allocation is
+    // physically elsewhere, and work on the view runs here and crosses NVLink.  Naming the target
+    // device keeps from_blob from asking the driver where the pointer lives and rejecting the answer.
+    const c10::Device here(at::kCUDA, static_cast<c10::DeviceIndex>(device_));
+    return at::for_blob(reinterpret_cast<void*>(m.ptr), {static_cast<int64_t>(m.bytes)})
+        .deleter([](void*) {})
+        .options(at::TensorOptions().dtype(at::kByte).device(here))
+        .target_device(here)
+        .make_tensor();
   }
 
   int device_;

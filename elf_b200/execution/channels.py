@@ -419,11 +419,18 @@ class ChannelTable:
         offsets, total = _arena_layout(sizes, self._roles, world, depth)
         if total == 0:
             return 0
-        arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
-        handle = symm_mem.rendezvous(arena, group=group.group_name)
-        arena.zero_()
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group=group)  # nobody raises a flag before every arena is zeroed
+        own_runtime = os.environ.get("ELF_B200_SYMM", "torch") == "vmm"
+        if own_runtime:
+            from ..parallel.symm import SymmetricBuffer
+
+            shared = SymmetricBuffer.allocate(total, torch.uint8, group, self.device)  # cleared, mapped by all, barrier done
+            arena, handle = shared.local, shared
+        else:
+            arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+            handle = symm_mem.rendezvous(arena, group=group.group_name)
+            arena.zero_()
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)  # nobody raises a flag before every arena is zeroed
         self._arena = (arena, handle)
         peers = {}
         switched = 0
@@ -433,7 +440,10 @@ class ChannelTable:
                 continue
             at_producer, at_consumer, slot = offsets[ch.index]
             if ch.peer_local not in peers:
-                peers[ch.peer_local] = (handle.get_buffer(ch.peer_local, (total,), torch.uint8), int(handle.buffer_ptrs[ch.peer_local]))
+                if own_runtime:
+                    peers[ch.peer_local] = (handle.peer_bytes(ch.peer_local), handle.peer_address(ch.peer_local))
+                else:
+                    peers[ch.peer_local] = (handle.get_buffer(ch.peer_local, (total,), torch.uint8), int(handle.buffer_ptrs[ch.peer_local]))
             peer_arena, peer_addr = peers[ch.peer_local]
             ch.attach_link(_CopyLink(ch, arena, peer_arena, peer_addr, at_producer, at_consumer, slot, depth, timeout_ms, ch.is_producer))
             switched += 1

@@ -62,6 +62,19 @@ class SymmetricBuffer:
     def peer_address(self, peer: int, byte_offset: int = 0) -> int:
         return self.addresses[peer] + byte_offset
 
+    def peer_bytes(self, peer: int) -> torch.Tensor:
+        """The buffer of rank ``peer`` as a uint8 tensor on this device (a mapping of the peer's
+        memory: copies into it cross NVLink)."""
+        nbytes = self.local.numel() * self.local.element_size()
+        if peer == self.rank:
+            return self.local.view(torch.uint8)
+        handle = getattr(self, "_handle", None)
+        if handle is None:
+            raise RuntimeError("this buffer has no peer mappings (single-process stand-in)")
+        if hasattr(handle, "peer_tensor"):  # own runtime: mappings are numbered in import order, i.e. by rank without this one
+            return handle.peer_tensor(peer if peer < self.rank else peer - 1)[:nbytes]
+        return handle.get_buffer(peer, (nbytes,), torch.uint8)
+
 
 def exchange_fds(my_fd: int, group) -> List[int]:
     """Give every other rank of ``group`` (processes of one node) a duplicate of ``my_fd`` and return

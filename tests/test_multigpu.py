@@ -12,8 +12,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def launch(case: str, nproc: int, timeout: int = 240):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def launch(case: str, nproc: int, timeout: int = 240, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(29600 + (os.getpid() % 300)), os.path.join(ROOT, "tests", "multigpu_worker.py"), case]
     out = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
@@ -35,6 +35,13 @@ def test_pipeline_stages_cut_inside_layers_two_gpus():
 
 def test_pipeline_copy_engine_transport_two_gpus():
     launch("pp_copy", 2)
+
+
+def test_own_symmetric_memory_runtime_under_gradient_exchange_and_copy_transport():
+    """The same two cases with the buffers allocated, exported and mapped by this package's
+    runtime on CUDA virtual memory (``ELF_B200_SYMM=vmm``) instead of torch's symmetric memory."""
+    launch("dp_symm", 2, ELF_B200_SYMM="vmm")
+    launch("pp_copy", 2, ELF_B200_SYMM="vmm")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
