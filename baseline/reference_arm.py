@@ -19,10 +19,8 @@ Known limits of the reference that shape this arm:
 from __future__ import annotations
 
 import json
-import math
 import os
 import sys
-import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")

@@ -16,7 +16,7 @@ from typing import Callable, Dict, List, Optional
 import torch
 import torch.distributed as dist
 
-from elf_b200.scheduling.scheduling import Operation, OperationType, OpOptions, compute_types
+from elf_b200.scheduling.scheduling import OperationType, OpOptions
 
 __all__ = [
     "bench",

@@ -18,7 +18,7 @@ synchronous copies on a CPU-only machine so the logic is testable without a GPU.
 from __future__ import annotations
 
 import logging
-from typing import Any, Dict, Iterable, List, Optional
+from typing import Any, Dict, Iterable, Optional
 from weakref import ref
 
 import torch

@@ -4,7 +4,6 @@ in ``elf_b200.models.llama`` is the one that runs on the sm_100a kernels."""
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List
 

@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import os
 
-from dataclasses import asdict, dataclass
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch

@@ -8,7 +8,7 @@ Llama-style models, which need RMSNorm, RoPE and SwiGLU instead.
 
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.nn.functional as F

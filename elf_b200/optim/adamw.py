@@ -12,9 +12,8 @@ On CPU tensors, or for dtypes other than bf16, the same class drives plain torch
 
 from __future__ import annotations
 
-import math
 import weakref
-from typing import Iterable, List, Optional
+from typing import Iterable, List
 
 import torch
 

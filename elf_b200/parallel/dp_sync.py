@@ -34,7 +34,7 @@ from ..ops import _ext
 from ..ops import gemm as _gemm
 from ..optim.flat import FlatGroup
 from ..zb_utils import LinearDW
-from .symm import LocalSymmetricGroup, SymmetricBuffer
+from .symm import SymmetricBuffer
 
 logger = logging.getLogger("dp_sync")
 

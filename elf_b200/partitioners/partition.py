@@ -15,9 +15,8 @@ scores, ``create_blocks()``, ``validate()``, ``to_image()``), as in the referenc
 from __future__ import annotations
 
 import logging
-from typing import Dict, List, Optional, Set, Tuple
+from typing import Dict, List, Optional, Set
 
-import torch
 import torch.fx as fx
 
 from ..registry import PARTITIONERS, resolve

@@ -17,7 +17,7 @@ Registered tracers (same keys as the reference, ``elf/partitioners/__init__.py:3
 from __future__ import annotations
 
 import logging
-from typing import Iterable, List, Sequence, Set
+from typing import Iterable, List, Set
 
 import torch
 import torch.nn as nn

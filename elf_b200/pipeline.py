@@ -30,7 +30,7 @@ import logging
 import os
 from dataclasses import dataclass, field, fields
 from datetime import timedelta
-from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, Iterator, List, Optional, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -43,10 +43,8 @@ from .partitioners.signature import Signature, sequential_signatures
 from .registry import COMM_SCHEDULERS, PARTITIONERS, SCHEDULERS, TRACERS, resolve
 from .scheduling import add_comms, check_schedule_validity, schedule_to_str
 from .scheduling.scheduling import OperationType
-from .utils.metadata import TensorMetadata
 from .utils.placement import Placement
 from .utils.shipping import broadcast_models, recv_models, send_models, transport_device
-from .zb_utils import LayerDW
 
 logger = logging.getLogger("pipeline")
 

@@ -7,7 +7,7 @@ In the reference this lives in the benchmark helpers only
 
 from __future__ import annotations
 
-from typing import Callable, Iterable, List, Optional, Set, Tuple
+from typing import Callable, List, Set, Tuple
 
 from ..registry import SCHEDULERS, resolve
 from .scheduling import Operation, OperationType, OpOptions, compute_types, per_rank_programs

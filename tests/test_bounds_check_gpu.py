@@ -8,7 +8,6 @@ import subprocess
 import sys
 
 import pytest
-import torch
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -11,7 +11,6 @@ fakes of the failing call.  Nothing here faults, traps or hangs a GPU.
 * the gradient-exchange epoch advances only on steps that exchange gradients.
 """
 
-import copy
 import os
 import time
 from datetime import timedelta

@@ -4,7 +4,6 @@ import copy
 
 import pytest
 import torch
-import torch.distributed as dist
 
 from tests.dist_utils import run_ranks
 

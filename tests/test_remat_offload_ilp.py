@@ -6,13 +6,12 @@ import os
 
 import pytest
 import torch
-import torch.nn as nn
 
-from elf_b200 import Pipeline, Placement, replace_layer_with_layer_dw
+from elf_b200 import Pipeline, replace_layer_with_layer_dw
 from elf_b200.execution.offload import OffloadToCPU, PinnedHostTensorPool
 from elf_b200.models.gpt import GPT, GPTConfig, gpt_stages
 from elf_b200.registry import SCHEDULERS
-from elf_b200.scheduling import OperationType, OpOptions, schedule_to_str, simulate
+from elf_b200.scheduling import OperationType, OpOptions, schedule_to_str
 from elf_b200.scheduling.ilp import AutoScheduler, RematScheduler, profile_all_stages, solve_remat, stagerematify
 from elf_b200.scheduling.offload_sched import offload_every
 
