@@ -83,3 +83,24 @@ def test_cut_allows_for_the_pipeline_fill():
     t1, ld1 = finish(skew)
     assert t1 < t0
     assert ld1[0] > ld1[-1] and sum(ld1) == pytest.approx(sum(ld0))
+
+
+def test_cut_granularity_by_simulated_step_and_first_rank_margin():
+    """With the number of micro-batches known, halves against thirds is decided by laying both cuts
+    out as ZB-V and simulating the step; rank 0 is kept a little lighter than the busiest rank."""
+    import elf_b200.models.llama as L
+
+    cm = LlamaCostModel(attention=0.315, mlp_up=0.4625, mlp_down=0.2225, head=1.9, embed=0.024, layer_ms=5.6, fbw=(0.331, 0.409, 0.26), source="measured", micro_batches=16)
+    pl = v(8)
+    halves, thirds = L._simulated_step(CFG, 16, pl, True, cm), L._simulated_step(CFG, 16, pl, "thirds", cm)
+    assert halves > 0 and thirds > 0
+    expected = "thirds" if thirds < (1.0 - L.THIRDS_GAIN) * halves else True
+    assert choose_llama_cut(CFG, 16, pl, cm) == expected
+    assert choose_llama_cut(CFG, 16, pl, cm) == choose_llama_cut(CFG, 16, pl, LlamaCostModel.from_dict(cm.to_dict()))  # every rank decides alike
+    for mode in (True, "thirds"):
+        ld = loads(llama_stage_costs(CFG, 16, pl, mode, cm), pl)
+        assert ld[0] <= max(ld[1:]) + 1e-9, ld  # rank 0 runs the head, the loss and the first and last operation of a step
+        assert max(ld) / (sum(ld) / len(ld)) < 1.05
+    # without the number of micro-batches the rule of thumb (busiest rank) still answers
+    cm.micro_batches = None
+    assert choose_llama_cut(CFG, 16, pl, cm) in (True, "thirds")
