@@ -10,7 +10,7 @@ durations and the order each rank really ran them in, are replayed by the timeli
 (``elf_b200.scheduling.simulator``) with a given hop latency, which shows how much of the
 measured step the data-flow model explains.
 
-    python benchmarks/pipeline_timeline.py timeline.json [--hop-ms 0.15]
+    python benchmarks/pipeline_timeline.py timeline.json [--hop-ms 0.15] [--chrome-trace trace.json]
 """
 
 from __future__ import annotations
@@ -97,11 +97,33 @@ def replay(placement, nmb, ranks, hop_ms):
     return res
 
 
+def chrome_trace(path_in: str, path_out: str) -> int:
+    """Write every timed operation of every rank as a complete event of the Trace Event format
+    (one process per rank; open the file in Perfetto or ``chrome://tracing``).  Returns the
+    number of events."""
+    with open(path_in) as f:
+        data = json.load(f)
+    colours = {"forward": "good", "backward_inputs": "bad", "backward": "terrible", "backward_params": "olive", "loss_forward": "yellow"}
+    events = []
+    for r, entry in sorted(data["ranks"].items(), key=lambda kv: int(kv[0])):
+        events.append({"ph": "M", "pid": int(r), "name": "process_name", "args": {"name": f"rank {r}"}})
+        for name, (t0, t1) in entry["timeline"].items():
+            kind = name.split("(")[0].split("#")[0]
+            events.append({"ph": "X", "pid": int(r), "tid": 0, "name": name.split("#")[0], "cat": kind, "ts": 1e6 * t0, "dur": 1e6 * max(0.0, t1 - t0),
+                           "cname": colours.get(kind, "grey")})
+    with open(path_out, "w") as f:
+        json.dump({"traceEvents": events, "displayTimeUnit": "ms"}, f)
+    return sum(1 for e in events if e["ph"] == "X")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("file")
     ap.add_argument("--hop-ms", type=float, nargs="*", default=[0.0, 0.1, 0.2, 0.4])
+    ap.add_argument("--chrome-trace", metavar="OUT", help="also write the operations as a Trace Event file (Perfetto / chrome://tracing)")
     args = ap.parse_args()
+    if args.chrome_trace:
+        print(f"wrote {chrome_trace(args.file, args.chrome_trace)} events to {args.chrome_trace}")
     placement, nmb, ranks = load(args.file)
     step_end, rows = analyse(placement, ranks)
     print(f"placement {placement}, {nmb} micro-batches; last operation ends {step_end:.1f} ms after the step's start")

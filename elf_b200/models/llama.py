@@ -390,6 +390,9 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
                 acc += fronts[r]
             # rank 0 runs the first forward and the last backward of a step and is never idle in
             # between: what it is given beyond its share delays everybody, so a margin is kept free
+            # (measured on three 4- and 8-GPU boxes: its work ran 0.1, 0.3 and 0.5 layer units per
+            # micro-batch over what the block times predicted - the loss, launch gaps, and a GPU
+            # that never idles clocks lowest under the power limit)
             offsets[0] = FIRST_RANK_MARGIN
             again = _v_bottleneck_bounds(prefix, n_ranks, head_units, rank_offsets=offsets)
             if again is None or again == bounds:
@@ -432,7 +435,7 @@ def half_layer_ranges(n_layers: int, n_stages: int, placement: Optional[Sequence
 
 
 THIRDS_GAIN = 0.02  # simulated gain below which a cut with three points per layer is not worth its two-tensor boundaries
-FIRST_RANK_MARGIN = 0.15  # layer units per micro-batch kept free on rank 0 of a V placement when the cut allows for the pipeline's fill
+FIRST_RANK_MARGIN = 0.3  # layer units per micro-batch kept free on rank 0 of a V placement when the cut allows for the pipeline's fill
 BOTTLENECK_SLACK = 0.005  # partitions whose busiest rank is this close to the smallest possible one compete on the second criterion
 LOAD_WEIGHT = 8.0  # weight of squared rank loads against squared stage costs when choosing among partitions within the bottleneck
 
