@@ -393,10 +393,10 @@ class ChannelTable:
         1. the ranks gather the largest message every channel has carried;
         2. every rank allocates ONE symmetric arena - the consuming end of a channel holds its ring
            (``depth`` slots) and a flag, the producing end a flag - and the group maps the arenas in
-           a single rendezvous.  (One
-           rendezvous per pipeline, entered by all of its ranks: the exchange behind it numbers its
-           rounds per process, so ranks that had rendezvoused pairwise a different number of times
-           would never meet.)
+           a single rendezvous.  (One rendezvous per pipeline, entered by all of its ranks: the
+           exchange behind it numbers its rounds per process, so ranks that had rendezvoused
+           pairwise a different number of times would never meet.)  ``ELF_B200_SYMM=vmm`` takes the
+           arena from this package's own runtime instead (``elf_b200.parallel.symm``).
         3. each channel end gets a link onto its region: the consumer's arena holds the ring, the
            producer writes it through its mapping of that arena.
 
