@@ -137,8 +137,17 @@ def _allocate_vmm(numel: int, dtype: torch.dtype, group, device) -> "SymmetricBu
     finally:
         os.close(fd)
     addresses = [0] * world
-    for peer in range(world):
-        addresses[peer] = arena.address if peer == rank else arena.peer_address(arena.import_peer(theirs[peer]))
+    try:
+        for peer in range(world):
+            if peer == rank:
+                addresses[peer] = arena.address
+                continue
+            fd, theirs[peer] = theirs[peer], -1  # import_peer closes the descriptor, whatever happens
+            addresses[peer] = arena.peer_address(arena.import_peer(fd))
+    finally:
+        for fd in theirs:  # descriptors that were never imported (an earlier import failed)
+            if fd >= 0:
+                os.close(fd)
     local = arena.tensor()[:nbytes].view(dtype)
     buf = SymmetricBuffer(local, addresses, rank)
     buf._handle = arena  # owns the allocation and the peer mappings
