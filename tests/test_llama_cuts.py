@@ -104,3 +104,29 @@ def test_cut_granularity_by_simulated_step_and_first_rank_margin():
     # without the number of micro-batches the rule of thumb (busiest rank) still answers
     cm.micro_batches = None
     assert choose_llama_cut(CFG, 16, pl, cm) in (True, "thirds")
+
+
+def test_cuts_for_random_cost_models_cover_the_model():
+    """Whatever the measured block times say, the cut is a contiguous cover of all layer parts, the
+    stage costs add up, and the granularity choice answers."""
+    import random
+
+    rng = random.Random(2)
+    done = 0
+    while done < 12:
+        cfg = LLAMA_CONFIGS[rng.choice(["llama3-8b", "llama-1.3b", "llama-13b", "llama-tiny"])]
+        p = rng.choice((2, 4, 8))
+        if 2 * p > 2 * cfg.n_layers:
+            continue
+        a, u = rng.uniform(0.15, 0.45), rng.uniform(0.3, 0.5)
+        f = rng.uniform(0.25, 0.4)
+        cm = LlamaCostModel(attention=a, mlp_up=u, mlp_down=1 - a - u, head=rng.uniform(0.3, 3.0), embed=rng.uniform(0, 0.3), layer_ms=rng.uniform(0.5, 10),
+                            fbw=(f, 0.4, 0.6 - f), source="measured", micro_batches=rng.choice((None, 2 * p, 16)))
+        pl = v(p)
+        for mode in (True, "thirds"):
+            ranges, k, costs = llama_stage_ranges(cfg, 2 * p, pl, mode, cm)
+            assert ranges[0][0] == 0 and ranges[-1][1] == k * cfg.n_layers
+            assert all(x[1] == y[0] and x[1] > x[0] for x, y in zip(ranges, ranges[1:]))
+            assert abs(sum(costs) - (cfg.n_layers + cm.head + cm.embed)) < 1e-6
+        assert choose_llama_cut(cfg, 2 * p, pl, cm) in (True, "thirds")
+        done += 1
